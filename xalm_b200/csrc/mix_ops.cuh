@@ -83,11 +83,11 @@ struct SeqStep {
 // ---- embedding -> streams -------------------------------------------------------------------------------------------------
 template <typename WT>
 __global__ void embed_streams_kernel(const WT* __restrict__ table, const int* __restrict__ tokens, int width, int S, size_t stream_stride,
-                                     float* __restrict__ xs) {
+                                     float* __restrict__ xs, float scale = 1.f) {
 	const int t = blockIdx.x;
 	const WT* row = table + (size_t) tokens[t] * width;
 	for (int c = threadIdx.x; c < width; c += blockDim.x) {
-		const float v = ldf(row + c);
+		const float v = ldf(row + c) * scale; // scale 1: the row as it is
 		for (int s = 0; s < S; s++) xs[(size_t) s * stream_stride + (size_t) t * width + c] = v;
 	}
 }
@@ -152,12 +152,24 @@ __global__ void hc_norm_kernel(const float* __restrict__ xs, int S, size_t strea
 }
 
 // ---- fused epilogues of the row products -------------------------------------------------------------------------------------
-enum { EPI_STORE = 0, EPI_SPLIT_KV = 1, EPI_GLU = 2, EPI_HC = 3 };
+enum { EPI_STORE = 0, EPI_SPLIT_KV = 1, EPI_GLU = 2, EPI_HC = 3, EPI_ACT = 4 };
 enum { GLU_CLAMPED = 0, GLU_SILU = 1, GLU_GELU_TANH = 2 };
+enum { ACT_NONE = 0, ACT_RELU_SQUARED = 1, ACT_SIGMOID = 2, ACT_SILU = 3 };
 struct RowsEpi {
 	int kind = EPI_STORE;
-	float* out = nullptr; // STORE / SPLIT_KV: (T, ldo); GLU: (T, ldo) with ldo = N / 2
+	float* out = nullptr; // STORE / SPLIT_KV / ACT: (T, ldo); GLU: (T, ldo) with ldo = N / 2
 	int ldo = 0;
+	// STORE: v <- cap * tanh(v / cap) when cap > 0 (soft-capped logits); then v <- v * mul_act(mul[row * ldm + col]) when mul is set (an
+	// output gate computed from the same input as the product's operand)
+	float cap = 0.f;
+	const float* mul = nullptr;
+	int ldm = 0, mul_act = ACT_SIGMOID;
+	// ACT: v <- act(v), no gate
+	int act = ACT_NONE;
+	// batched products (blockIdx.z = b): A advances by batch_a floats, W by batch_w elements, the output (and mul) by batch_o columns.
+	// One launch then runs a product per head on that head's slice of the rows.
+	int batch_a = 0, batch_o = 0;
+	size_t batch_w = 0;
 	// SPLIT_KV: columns [n_plain, n_plain + kdim) are the step's keys, the next vdim its values; they go to ring slot (pos0 + row) % ring
 	int n_plain = 0, kdim = 0, vdim = 0, ring = 1, cache_f32 = 0;
 	void* kc = nullptr;
@@ -187,6 +199,12 @@ __device__ __forceinline__ float glu_clamped(float g, float u, float limit, floa
 	return g * sigmoidf_(alpha * g) * (u + 1.f);
 }
 
+__device__ __forceinline__ float act_apply(int act, float v) {
+	if (act == ACT_RELU_SQUARED) { v = fmaxf(v, 0.f); return v * v; }
+	if (act == ACT_SIGMOID) return sigmoidf_(v);
+	if (act == ACT_SILU) return v * sigmoidf_(v);
+	return v;
+}
 __device__ __forceinline__ float gelu_tanhf_(float z) { return 0.5f * z * (1.f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z))); }
 __device__ __forceinline__ float glu_apply(int act, float g, float u, float limit, float alpha) {
 	if (act == GLU_SILU) return g * sigmoidf_(g) * u;
@@ -212,7 +230,12 @@ __device__ __forceinline__ void hc_write(const RowsEpi& e, int row, int col, int
 // one value (for the pairwise GLU: called with the even column and both values)
 __device__ __forceinline__ void epi_apply(const RowsEpi& e, int row, int col, int N, float v, float v_next) {
 	switch (e.kind) {
-		case EPI_STORE: e.out[(size_t) row * e.ldo + col] = v; break;
+		case EPI_STORE:
+			if (e.cap > 0.f) v = e.cap * tanhf(v / e.cap);
+			if (e.mul) v *= act_apply(e.mul_act, e.mul[(size_t) row * e.ldm + col]);
+			e.out[(size_t) row * e.ldo + col] = v;
+			break;
+		case EPI_ACT: e.out[(size_t) row * e.ldo + col] = act_apply(e.act, v); break;
 		case EPI_SPLIT_KV: {
 			if (col < e.n_plain) {
 				if (col >= e.silu_off && col < e.silu_off + e.silu_n) v = v * sigmoidf_(v);
@@ -245,6 +268,12 @@ __device__ __forceinline__ void epi_apply(const RowsEpi& e, int row, int col, in
 template <typename WT>
 __global__ void __launch_bounds__(256) rows_gemm_kernel(const float* __restrict__ A, int lda, const WT* __restrict__ W, int T, int N, int K, RowsEpi e) {
 	constexpr int BM = 64, BN = 64, BK = 16;
+	if (blockIdx.z) { // one product of a batch
+		A += (size_t) blockIdx.z * e.batch_a;
+		W += (size_t) blockIdx.z * e.batch_w;
+		e.out += (size_t) blockIdx.z * e.batch_o;
+		if (e.mul) e.mul += (size_t) blockIdx.z * e.batch_o;
+	}
 	__shared__ float As[BK][BM + 4];
 	__shared__ float Ws[BK][BN + 4];
 	const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
@@ -310,6 +339,12 @@ static __global__ void rows_epilogue_kernel(const float* __restrict__ src, int l
 template <typename WT, int TB, int KS>
 __global__ void __launch_bounds__(256) rows_matvec_kernel(const float* __restrict__ A, int lda, const WT* __restrict__ W, int T, int N, int K, RowsEpi e) {
 	__shared__ float red[8][TB][2];
+	if (blockIdx.z) { // one product of a batch
+		A += (size_t) blockIdx.z * e.batch_a;
+		W += (size_t) blockIdx.z * e.batch_w;
+		e.out += (size_t) blockIdx.z * e.batch_o;
+		if (e.mul) e.mul += (size_t) blockIdx.z * e.batch_o;
+	}
 	const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, ks = warp % KS;
 	const int pair = blockIdx.x * (8 / KS) + warp / KS;
 	const int c0 = pair * 2;
@@ -318,7 +353,7 @@ __global__ void __launch_bounds__(256) rows_matvec_kernel(const float* __restric
 	if (live) {
 		const WT* w0 = W + (size_t) c0 * K;
 		const WT* w1 = W + (size_t) (two ? c0 + 1 : c0) * K;
-		const bool vec = (K % 8 == 0) && (lda % 4 == 0) && ((reinterpret_cast<uintptr_t>(W) & 31) == 0) && ((reinterpret_cast<uintptr_t>(A) & 15) == 0);
+		const bool vec = (K % 8 == 0) && (lda % 4 == 0) && ((reinterpret_cast<uintptr_t>(W) & 31) == 0) && ((reinterpret_cast<uintptr_t>(A) & 15) == 0); // of this batch's slices
 		if (vec) {
 #pragma unroll 2
 			for (int k = (ks * 32 + lane) * 8; k < K; k += 256 * KS) {
@@ -387,6 +422,8 @@ struct SwaArgs {
 	int ldq, q_off, ldg, g_off;
 	const void* kc;    // ring (ring, G * d)
 	const void* vc;    // ring (ring, G * dv)
+	int ldk, ldv;      // elements between the rows of two slots; 0: G * d and G * dv.  A cache whose rows hold more than the keys (values that
+	                   // are a slice of the key row: vc points into kc with ldv = ldk) is read in place
 	int ring;
 	int H, G, d, dv;
 	int window;        // position i sees j with 0 <= i - j < window
@@ -510,7 +547,8 @@ __global__ void __launch_bounds__(256) swa_attn_kernel(SwaArgs a) {
 	const CT* kc = reinterpret_cast<const CT*>(a.kc);
 	const CT* vc = reinterpret_cast<const CT*>(a.vc);
 	const int t = blockIdx.x, sp = blockIdx.y, tid = threadIdx.x, nth = blockDim.x, lane = tid & 31, warp = tid >> 5, nw = nth >> 5;
-	const bool vec8 = ((d | (G * d)) & 7) == 0;
+	const int ldk = a.ldk ? a.ldk : G * d, ldv = a.ldv ? a.ldv : G * dv;
+	const bool vec8 = ((d | ldk) & 7) == 0 && (reinterpret_cast<uintptr_t>(a.kc) & 31) == 0;
 	if (t >= a.step->n) return;
 	const int i = a.step->pos0 + t;
 	const SwaKeys km = swa_keys(a.window, a.keep_first, a.ring, i);
@@ -528,12 +566,12 @@ __global__ void __launch_bounds__(256) swa_attn_kernel(SwaArgs a) {
 		for (int x = tid; x < nb * kch; x += nth) {
 			const int jj = x / kch, c = (x % kch) * EPC;
 			const unsigned dst = (unsigned) __cvta_generic_to_shared(Ks + (size_t) jj * (G * d) + c);
-			asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(kc + (size_t) km.slot(j0 + jj) * (G * d) + c) : "memory");
+			asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(kc + (size_t) km.slot(j0 + jj) * ldk + c) : "memory");
 		}
 		for (int x = tid; x < nb * vch; x += nth) {
 			const int jj = x / vch, c = (x % vch) * EPC;
 			const unsigned dst = (unsigned) __cvta_generic_to_shared(Vs + (size_t) jj * (G * dv) + c);
-			asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(vc + (size_t) km.slot(j0 + jj) * (G * dv) + c) : "memory");
+			asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(vc + (size_t) km.slot(j0 + jj) * ldv + c) : "memory");
 		}
 		asm volatile("cp.async.commit_group;" ::: "memory");
 	};
@@ -572,7 +610,7 @@ __global__ void __launch_bounds__(256) swa_attn_kernel(SwaArgs a) {
 #pragma unroll
 					for (int kq = 0; kq < 4; kq++) {
 						const int jj = warp + kq * 8;
-						const CT* kr = (staged ? Ks + (size_t) jj * (G * d) : kc + (size_t) km.slot(j0 + min(jj, nb - 1)) * (G * d)) + g * d + c;
+						const CT* kr = (staged ? Ks + (size_t) jj * (G * d) : kc + (size_t) km.slot(j0 + min(jj, nb - 1)) * ldk) + g * d + c;
 						if (jj < nb && vec8) ld8(kr, kk[kq]);
 						else
 #pragma unroll
@@ -658,7 +696,7 @@ __global__ void __launch_bounds__(256) swa_attn_kernel(SwaArgs a) {
 				for (int jb8 = 0; jb8 < nb; jb8 += 8) { // eight loads in flight
 					float v[8];
 #pragma unroll
-					for (int e8 = 0; e8 < 8; e8++) v[e8] = jb8 + e8 < nb ? ldf(vcol + (size_t) (staged ? jb8 + e8 : km.slot(j0 + jb8 + e8)) * (G * dv)) : 0.f;
+					for (int e8 = 0; e8 < 8; e8++) v[e8] = jb8 + e8 < nb ? ldf(vcol + (staged ? (size_t) (jb8 + e8) * (G * dv) : (size_t) km.slot(j0 + jb8 + e8) * ldv)) : 0.f;
 #pragma unroll
 					for (int e8 = 0; e8 < 8; e8++)
 #pragma unroll
@@ -728,7 +766,7 @@ __host__ __device__ inline size_t swa_tile_smem_floats(int H, int G, int d, int 
 template <typename CT>
 __device__ __forceinline__ void swa_load_tile(float* dst, int ldd, const CT* base, int row_elems, int col0, int w, int wp, int j0, int nbk, const SwaKeys& km,
                                               int tid, int nth) {
-	if (((w | row_elems | col0) & 7) == 0) {
+	if (((w | row_elems | col0) & 7) == 0 && (reinterpret_cast<uintptr_t>(base) & 31) == 0) {
 		const int cpr = w >> 3, total = SWA_KB * cpr;
 		for (int x0 = tid; x0 < total; x0 += 2 * nth) {
 			float v[2][8];
@@ -899,7 +937,7 @@ __global__ void __launch_bounds__(256) swa_tile_kernel(SwaArgs a) {
 		// ---- raw scores, one kv group at a time ----
 		for (int g = 0; g < G; g++) {
 			__syncthreads(); // the last reader of KV (and, on the first pass, the set-up above) is done
-			swa_load_tile(KV, ldkv, kc, G * d, g * d, d, dp, j0, nbk, km, tid, nth);
+			swa_load_tile(KV, ldkv, kc, a.ldk ? a.ldk : G * d, g * d, d, dp, j0, nbk, km, tid, nth);
 			__syncthreads();
 			if (kt == 4) swa_qk_tiles<4, 4>(a, Qs, KV, Sc, g, Rg, R, ldq, ldkv, dp, TQ, rep, nq, nbk, i_lo, j0, km, tid, nth);
 			else if (kt == 2) swa_qk_tiles<2, 4>(a, Qs, KV, Sc, g, Rg, R, ldq, ldkv, dp, TQ, rep, nq, nbk, i_lo, j0, km, tid, nth);
@@ -952,7 +990,7 @@ __global__ void __launch_bounds__(256) swa_tile_kernel(SwaArgs a) {
 		// ---- O <- alpha O + P^T V, one kv group at a time ----
 		for (int g = 0; g < G; g++) {
 			__syncthreads(); // probabilities written; the last reader of KV is done
-			swa_load_tile(KV, ldkv, vc, G * dv, g * dv, dv, dvp, j0, nbk, km, tid, nth);
+			swa_load_tile(KV, ldkv, vc, a.ldv ? a.ldv : G * dv, g * dv, dv, dvp, j0, nbk, km, tid, nth);
 			__syncthreads();
 			if ((Rg >> 2) * (dvp >> 2) >= nth) swa_pv_tiles<4>(Pr, KV, O, alpha, g, Rg, R, ldkv, dvp, tid, nth);
 			else swa_pv_tiles<2>(Pr, KV, O, alpha, g, Rg, R, ldkv, dvp, tid, nth);
@@ -993,6 +1031,14 @@ struct Hgrn2Args {
 	float* out;          // (T, H * dv)
 	int max_rows;        // most tokens a step can bring (the launch sizes its shared memory by it)
 	int activated;       // 1: proj already holds the forget gate and silu(q) (the producing product's epilogue applied them)
+	// Retention: with `decay` set the recurrence is S_t = decay[h] S_{t-1} + (k_scale k_t) v_t^T, o_t = S_t^T q_t: one fixed decay per head, keys
+	// of their own at k_off + h * d, q taken as it is (f_off, f_bias, lower and activated are not read)
+	const float* decay;  // (H) or NULL
+	int k_off;
+	float k_scale;
+	int norm_plain;      // 1: o over its root mean square with no weight (norm_w NULL)
+	const float* gate;   // (T, ldg): o <- o * silu(gate[t, g_off + h * dv + c]) after the norm; NULL: none
+	int ldg, g_off;
 };
 constexpr int HG_TC = 8; // tokens staged at a time
 
@@ -1002,7 +1048,8 @@ static __global__ void hgrn2_kernel(Hgrn2Args a) {
 	float* S = sm;                  // d * dv
 	float* fch = S + (size_t) d * dv; // TC * d
 	float* qch = fch + HG_TC * d;   // TC * d
-	float* och = qch + HG_TC * d;   // TC * dv
+	float* gch = qch + HG_TC * d;   // TC * d  what multiplies v: 1 - f, or the key
+	float* och = gch + HG_TC * d;   // TC * dv
 	float* st = a.state + (size_t) h * d * dv;
 	for (int x = tid; x < d * dv; x += nth) S[x] = st[x];
 	const int T = a.step->n;
@@ -1012,10 +1059,17 @@ static __global__ void hgrn2_kernel(Hgrn2Args a) {
 		for (int x = tid; x < nt * d; x += nth) {
 			const int tt = x / d, i = x % d;
 			const float* row = a.proj + (size_t) (t0 + tt) * a.ld;
+			const float zq = row[a.q_off + h * d + i];
+			if (a.decay) {
+				fch[x] = a.decay[h];
+				gch[x] = row[a.k_off + h * d + i] * a.k_scale;
+				qch[x] = zq;
+				continue;
+			}
 			const float z = row[a.f_off + h * d + i] + (a.f_bias && !a.activated ? a.f_bias[h * d + i] : 0.f);
 			const float lo = a.lower ? a.lower[h * d + i] : 0.f;
 			fch[x] = a.activated ? z : lo + (1.f - lo) * sigmoidf_(z);
-			const float zq = row[a.q_off + h * d + i];
+			gch[x] = 1.f - fch[x];
 			qch[x] = a.activated ? zq : zq * sigmoidf_(zq);
 		}
 		__syncthreads();
@@ -1024,10 +1078,11 @@ static __global__ void hgrn2_kernel(Hgrn2Args a) {
 				const float v = a.proj[(size_t) (t0 + tt) * a.ld + a.v_off + h * dv + c];
 				const float* f = fch + tt * d;
 				const float* q = qch + tt * d;
+				const float* gk = gch + tt * d;
 				float o = 0.f;
 				for (int i = 0; i < d; i++) {
 					const float fi = f[i];
-					const float s = fmaf(fi, S[(size_t) i * dv + c], (1.f - fi) * v);
+					const float s = fmaf(fi, S[(size_t) i * dv + c], gk[i] * v);
 					S[(size_t) i * dv + c] = s;
 					o = fmaf(s, q[i], o);
 				}
@@ -1038,20 +1093,25 @@ static __global__ void hgrn2_kernel(Hgrn2Args a) {
 		for (int tt = tid >> 5; tt < nt; tt += nth >> 5) {
 			const int lane = tid & 31;
 			float r = 1.f;
-			if (a.norm_w) {
+			if (a.norm_w || a.norm_plain) {
 				float ss = 0.f;
 				for (int c = lane; c < dv; c += 32) ss = fmaf(och[tt * dv + c], och[tt * dv + c], ss);
 				ss = warp_sum(ss);
 				r = 1.f / sqrtf(ss / (float) dv + a.eps);
 			}
 			float* orow = a.out + (size_t) (t0 + tt) * (a.H * dv) + h * dv;
-			for (int c = lane; c < dv; c += 32) orow[c] = och[tt * dv + c] * r * (a.norm_w ? a.norm_w[c] : 1.f);
+			const float* grow = a.gate ? a.gate + (size_t) (t0 + tt) * a.ldg + a.g_off + h * dv : nullptr;
+			for (int c = lane; c < dv; c += 32) {
+				float o = och[tt * dv + c] * r * (a.norm_w ? a.norm_w[c] : 1.f);
+				if (grow) o *= grow[c] * sigmoidf_(grow[c]);
+				orow[c] = o;
+			}
 		}
 	}
 	__syncthreads();
 	for (int x = tid; x < d * dv; x += nth) st[x] = S[x];
 }
-inline size_t hgrn2_smem_bytes(int d, int dv) { return sizeof(float) * ((size_t) d * dv + 2 * (size_t) HG_TC * d + (size_t) HG_TC * dv); }
+inline size_t hgrn2_smem_bytes(int d, int dv) { return sizeof(float) * ((size_t) d * dv + 3 * (size_t) HG_TC * d + (size_t) HG_TC * dv); }
 
 // ---- the same recurrence, the state's columns spread over warps, CTAs and a thread-block cluster ---------------------------------
 // Column c of a head's state evolves on its own: S[:, c] <- f .* S[:, c] + (1 - f) v[c], o[c] = q . S[:, c].  A warp owns HG_CW columns
@@ -1110,7 +1170,7 @@ __global__ void hgrn2_cols_kernel(Hgrn2Args a) {
 			rf[u] = 0.f; rq[u] = 0.f;
 			if (x < HG_TT * DP && tt < nt && i < d) {
 				const float* row = a.proj + (size_t) (t0 + tt) * a.ld;
-				rf[u] = row[a.f_off + h * d + i];
+				rf[u] = row[(a.decay ? a.k_off : a.f_off) + h * d + i];
 				rq[u] = row[a.q_off + h * d + i];
 			}
 		}
@@ -1125,13 +1185,16 @@ __global__ void hgrn2_cols_kernel(Hgrn2Args a) {
 			if (x < HG_TT * DP) {
 				float f = 0.f, g = 0.f, q = 0.f;
 				if (tt < nt && i < d) {
-					if (a.activated) { f = rf[u]; q = rq[u]; }
+					if (a.decay) { f = a.decay[h]; g = rf[u] * a.k_scale; q = rq[u]; }
 					else {
-						const float lo = a.lower ? a.lower[h * d + i] : 0.f;
-						f = lo + (1.f - lo) * sigmoidf_(rf[u] + (a.f_bias ? a.f_bias[h * d + i] : 0.f));
-						q = rq[u] * sigmoidf_(rq[u]);
+						if (a.activated) { f = rf[u]; q = rq[u]; }
+						else {
+							const float lo = a.lower ? a.lower[h * d + i] : 0.f;
+							f = lo + (1.f - lo) * sigmoidf_(rf[u] + (a.f_bias ? a.f_bias[h * d + i] : 0.f));
+							q = rq[u] * sigmoidf_(rq[u]);
+						}
+						g = 1.f - f;
 					}
-					g = 1.f - f;
 				}
 				buf[x] = f; buf[HG_TT * DP + x] = g; buf[2 * HG_TT * DP + x] = q;
 			}
@@ -1197,16 +1260,25 @@ __global__ void hgrn2_cols_kernel(Hgrn2Args a) {
 			const int i = lane + 32 * k, c = c0 + cc;
 			if (i < d && c < dv) st[(size_t) i * dv + c] = S[cc][k];
 		}
-	if (!a.norm_w) return; // uniform over the cluster: nobody waits
+	const bool normed = a.norm_w || a.norm_plain;
+	if (!normed && !a.gate) return; // uniform over the cluster: nobody waits
 	cluster.sync();
 	const unsigned nb = cluster.num_blocks();
 	for (int t = warp; t < T; t += nw) {
-		float tot = lane < (int) nb ? cluster.map_shared_rank(ssq, lane)[t] : 0.f;
-		tot = warp_sum(tot);
-		const float r = 1.f / sqrtf(tot / (float) dv + a.eps);
+		float r = 1.f;
+		if (normed) {
+			float tot = lane < (int) nb ? cluster.map_shared_rank(ssq, lane)[t] : 0.f;
+			tot = warp_sum(tot);
+			r = 1.f / sqrtf(tot / (float) dv + a.eps);
+		}
 		float* orow = a.out + (size_t) t * (a.H * dv) + h * dv;
+		const float* grow = a.gate ? a.gate + (size_t) t * a.ldg + a.g_off + h * dv : nullptr;
 		for (int cc = lane; cc < cpb; cc += 32)
-			if (c_blk + cc < dv) orow[c_blk + cc] = orow[c_blk + cc] * r * a.norm_w[c_blk + cc];
+			if (c_blk + cc < dv) {
+				float o = orow[c_blk + cc] * r * (a.norm_w ? a.norm_w[c_blk + cc] : 1.f);
+				if (grow) o *= grow[c_blk + cc] * sigmoidf_(grow[c_blk + cc]);
+				orow[c_blk + cc] = o;
+			}
 	}
 	cluster.sync(); // no CTA leaves while another still reads its sums
 }
@@ -1323,12 +1395,13 @@ static inline int launch_check(const char* what) {
 static inline int norm_threads(int width) { return width >= 1024 ? 256 : width >= 256 ? 128 : 64; }
 
 // out(T,N) = A(T,K) . W(N,K)^T with epilogue e, IEEE fp32 arithmetic; W is bf16 or fp32
-static inline int launch_rows(const float* A, int lda, const void* W, bool w_bf16, int T, int N, int K, const RowsEpi& e, cudaStream_t s) {
+// batch > 1: that many products in one launch, operands and output advancing by e.batch_a / batch_w / batch_o per product
+static inline int launch_rows(const float* A, int lda, const void* W, bool w_bf16, int T, int N, int K, const RowsEpi& e, cudaStream_t s, int batch = 1) {
 	if (T <= 4) {
 		const int pairs = (N + 1) / 2;
 		int ks = 1; // warps per column pair: enough CTAs for two per SM, each slice of K at least 256 long
-		while (ks < 8 && (pairs * ks + 7) / 8 < 296 && K >= 512 * ks) ks *= 2;
-		const int grid = (pairs * ks + 7) / 8;
+		while (ks < 8 && (pairs * ks + 7) / 8 * batch < 296 && K >= 512 * ks) ks *= 2;
+		const dim3 grid((pairs * ks + 7) / 8, 1, batch);
 #define XALM_ROWS_MATVEC(WT_, TB_)                                                                                                   \
 	do {                                                                                                                             \
 		if (ks == 1) rows_matvec_kernel<WT_, TB_, 1><<<grid, 256, 0, s>>>(A, lda, (const WT_*) W, T, N, K, e);                       \
@@ -1345,7 +1418,7 @@ static inline int launch_rows(const float* A, int lda, const void* W, bool w_bf1
 		}
 #undef XALM_ROWS_MATVEC
 	} else {
-		const dim3 grid((N + 63) / 64, (T + 63) / 64);
+		const dim3 grid((N + 63) / 64, (T + 63) / 64, batch);
 		if (w_bf16) rows_gemm_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>(A, lda, (const __nv_bfloat16*) W, T, N, K, e);
 		else rows_gemm_kernel<float><<<grid, 256, 0, s>>>(A, lda, (const float*) W, T, N, K, e);
 	}
@@ -1636,7 +1709,8 @@ static inline int launch_swa(SwaArgs a, int rows, bool cache_f32, cudaStream_t s
 		size_t smem = swa_smem_bytes(a.H, a.d, a.dv);
 		const size_t staged = swa_stage_off(a.H, a.d, a.dv) * 4 + swa_stage_bytes(a.G, a.d, a.dv, cache_f32);
 		a.stage_off = 0;
-		if (((a.d | a.dv) & 7) == 0 && staged <= 200 * 1024) { // rows of whole 16-byte pieces, and room for a key block
+		const bool rows16 = ((a.d | a.dv | a.ldk | a.ldv) & 7) == 0 && ((reinterpret_cast<uintptr_t>(a.kc) | reinterpret_cast<uintptr_t>(a.vc)) & 15) == 0;
+		if (rows16 && staged <= 200 * 1024) { // rows of whole 16-byte pieces, and room for a key block
 			a.stage_off = (int) swa_stage_off(a.H, a.d, a.dv);
 			smem = staged;
 		}

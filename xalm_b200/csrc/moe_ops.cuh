@@ -1,9 +1,10 @@
 // moe_ops.cuh — a mixture of small gated feed-forward experts, as three mechanisms that another design can use on their own:
 //
-//   moe_router_kernel   per token: logits z = W_router h in fp32, scores s = sigmoid(z); optionally the experts form n_groups equal groups
-//                       of neighbours, a group scores the sum of its two largest s, and only experts of the keep_groups best groups can be
-//                       chosen; the `top` largest s among those are chosen (ties: the lower index), their weights are the scores
-//                       themselves (not renormalised)
+//   moe_router_kernel   per token: logits z = W_router h in fp32, scores s = sigmoid(z) or softmax(z) over all experts; optionally the
+//                       experts form n_groups equal groups of neighbours, a group scores the sum of its two largest s or its largest s, and
+//                       only experts of the keep_groups best groups can be chosen; the `top` largest s among those are chosen (ties: the
+//                       lower index); their weights are the scores themselves, or the scores over their sum
+//   moe_combine_kernel  x <- x + sum of a token's `top` expert rows with their weights, in slot order
 //   moe_sort_kernel     the step's (token, slot) pairs ordered by expert, cut into row tiles of one expert each
 //   moe_gemm_kernel     out[pair] = A[row of pair] . W_expert(pair)^T in IEEE fp32 for every tile, with the row products' fused epilogues
 //                       (gated activation on interleaved gate | up columns, plain store)
@@ -30,7 +31,13 @@ struct MoeRouteArgs {
 	int* idx;   // (T, top)
 	float* wgt; // (T, top)
 	const SeqStep* step;
+	int score_kind;  // MOE_SCORE_SIGMOID (0) or MOE_SCORE_SOFTMAX: exp(z - max z) / sum over all experts
+	int group_kind;  // MOE_GROUP_TOP2_SUM (0) or MOE_GROUP_MAX: what a group scores
+	int renormalise; // 1: the chosen weights are divided by (their sum + renorm_eps)
+	float renorm_eps;
 };
+enum { MOE_SCORE_SIGMOID = 0, MOE_SCORE_SOFTMAX = 1 };
+enum { MOE_GROUP_TOP2_SUM = 0, MOE_GROUP_MAX = 1 };
 
 // (value, index) argmax over a warp; ties go to the lower index; index -1 = nothing
 __device__ __forceinline__ void warp_argmax(float& v, int& i) {
@@ -67,10 +74,19 @@ __global__ void __launch_bounds__(256) moe_router_kernel(MoeRouteArgs a) {
 		} else
 			for (int k = lane; k < a.K; k += 32) z = fmaf(ldf(W + (size_t) e * a.K + k), hs[k], z);
 		z = warp_sum(z);
-		if (lane == 0) sc[e] = sigmoidf_(z);
+		if (lane == 0) sc[e] = a.score_kind == MOE_SCORE_SOFTMAX ? z : sigmoidf_(z);
 	}
 	__syncthreads();
 	if (warp != 0) return;
+	if (a.score_kind == MOE_SCORE_SOFTMAX) {
+		float zm = -INFINITY, den = 0.f;
+		for (int e = lane; e < a.E; e += 32) zm = fmaxf(zm, sc[e]);
+		zm = warp_max(zm);
+		for (int e = lane; e < a.E; e += 32) den += expf(sc[e] - zm);
+		den = warp_sum(den);
+		for (int e = lane; e < a.E; e += 32) sc[e] = expf(sc[e] - zm) / den;
+		__syncwarp();
+	}
 	const int ng = a.n_groups > 1 ? a.n_groups : 1, gsz = a.E / ng;
 	if (ng > 1) {
 		for (int g = lane; g < ng; g += 32) { // sum of the group's two largest scores
@@ -80,7 +96,7 @@ __global__ void __launch_bounds__(256) moe_router_kernel(MoeRouteArgs a) {
 				if (v > m1) { m2 = m1; m1 = v; }
 				else if (v > m2) m2 = v;
 			}
-			gsc[g] = gsz > 1 ? m1 + m2 : m1;
+			gsc[g] = (gsz > 1 && a.group_kind == MOE_GROUP_TOP2_SUM) ? m1 + m2 : m1;
 		}
 		for (int e = lane; e < a.E; e += 32) flag[e] = 0;
 		__syncwarp();
@@ -112,6 +128,40 @@ __global__ void __launch_bounds__(256) moe_router_kernel(MoeRouteArgs a) {
 		}
 		__syncwarp();
 	}
+	if (a.renormalise) {
+		float tot = 0.f;
+		for (int r = lane; r < a.top; r += 32) tot += a.wgt[(size_t) t * a.top + r]; // written by lane 0 above
+		tot = warp_sum(tot) + a.renorm_eps;
+		for (int r = lane; r < a.top; r += 32) a.wgt[(size_t) t * a.top + r] /= tot;
+	}
+}
+
+// ---- x <- x + sum_p w[t, p] y[row(t, p)]: the chosen experts' rows of a token joined in slot order (a fixed order: the same bits every run) ----
+struct MoeCombineArgs {
+	const float* y;      // (rows * top, ldy)
+	int ldy, top, width;
+	const float* wgt;    // (rows, top)
+	const int* part_row; // (rows, top) row of y that holds slot p of token t, or NULL: t * top + p
+	const float* x_in;   // (rows, width) or NULL
+	float* x_out;        // (rows, width); may be x_in
+	const SeqStep* step;
+};
+static __global__ void moe_combine_kernel(MoeCombineArgs a) {
+	const int t = blockIdx.x;
+	if (t >= a.step->n) return;
+	for (int c = threadIdx.x; c < a.width; c += blockDim.x) {
+		float v = 0.f;
+		for (int p = 0; p < a.top; p++) {
+			const size_t pk = (size_t) t * a.top + p;
+			v = fmaf(a.wgt[pk], a.y[(a.part_row ? (size_t) a.part_row[pk] : pk) * a.ldy + c], v);
+		}
+		const size_t at = (size_t) t * a.width + c;
+		a.x_out[at] = a.x_in ? a.x_in[at] + v : v;
+	}
+}
+static inline int launch_moe_combine(const MoeCombineArgs& a, int rows, cudaStream_t s) {
+	moe_combine_kernel<<<rows, norm_threads(a.width), 0, s>>>(a);
+	return launch_check("moe_combine");
 }
 
 constexpr int MOE_TM = 64; // rows of a tile

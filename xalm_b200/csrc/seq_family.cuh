@@ -1,4 +1,4 @@
-// seq_family.cuh — the sequence engine shared by the model families that a config.json describes (Nabalix, Bolovik): what a
+// seq_family.cuh — the sequence engine shared by the model families that a config.json describes (Nabalix, Bolovik, Duletar): what a
 // family does NOT write itself.
 //
 //   * tensors by name: the family lists what it reads (expect), the loader uploads them (any order, fp32 / fp16 / bf16), finalize
@@ -220,7 +220,7 @@ int tc_register(SeqModel* m, const WMat& wm, TcWeight* t) {
 // plane, or hi + lo with "seq_tc" = 2), fp32 accumulation, then the same epilogue as an elementwise kernel.
 int rows_product(SeqModel* m, const float* A, int lda, const void* W, const TcWeight* tw, int T, int N, int K, const RowsEpi& e, int* nl) {
 	if (m->use_tc && tw && tw->hi && T >= m->tc_min_rows && lda == K) {
-		if (e.kind == EPI_STORE && e.ldo % 4 == 0) {
+		if (e.kind == EPI_STORE && e.ldo % 4 == 0 && e.cap == 0.f && !e.mul) { // nothing to do to the product: the GEMM stores it itself
 			*nl += 2;
 			return tc_gemm(*tw, A, T, e.out, e.ldo, m->a_hi, m->a_lo, m->stream);
 		}
