@@ -180,6 +180,31 @@ int xalm_cuda_delta_rule(float* out, float* state, float* conv_state, const floa
 int xalm_cuda_moe_ffn(float* out_pairs, int* idx, float* wgt, const float* h, const float* w_router, const float* w_gate, const float* w_up,
                       const float* w_down, int T, int K, int E, int top, int ff, int n_groups, int keep_groups, int act, int w_bf16);
 
+/* Mechanisms of the latent-attention / retention designs, as ops (host arrays in and out, the same kernels the families run):
+ * moe_ffn_routed: moe_ffn with the router's variants.  score_kind 0: sigmoid, 1: softmax over all experts; group_kind 0: a group scores the
+ *   sum of its two largest s, 1: its largest; renormalise 1: the chosen scores over (their sum + 1e-20); act 0: the clamped gate
+ *   min(g, limit) sigmoid(1.702 .) (clamp(u, +-limit) + 1), 1 silu, 2 tanh-gelu; x_io (T, K) or NULL: x_io += sum over a token's slots of
+ *   wgt * out_pairs.
+ * retention: per head S <- decay[h] S + (k_scale k_t) v_t^T, o_t = S^T q_t for T tokens from position pos0; q and k (T, H d) are turned first
+ *   (the first 2 rot_half entries of a head, entry i with i + rot_half, angle = position * freq[i]); o over its root mean square (eps, no
+ *   weight), times silu(gate) when gate (T, H dv) is given.  state (H, d, dv) is read and written.
+ * latent_post: proj (T, q_rank + kv_rank + rot) -> cq_out (T, q_rank) = rmsnorm(proj[:, :q_rank]) q_norm; cache row of position p (slot
+ *   p % ring of cache_out (ring, kv_rank + rot)) = [rmsnorm(kv latent) kv_norm | the rot shared key entries turned by p].
+ * latent_attend: causal softmax attention of H heads over cache rows (pos0 + T, ld) whose first R entries are the latent c and next r the
+ *   turned shared key: score = scale (q_h[:d] . (uk_h c) + turn(q_h[d:]) . k_rot), out_h = uv_h (sum_j p_j c_j), times sigmoid(gate) when
+ *   given.  q (T, H (d + r)) un-turned, uk (H d, R), uv (H dv, R).  n_splits 0: the launcher chooses.
+ * rows_act: out = act(x W^T) (act 1 relu squared, 2 sigmoid, 3 silu) or, with act 0, cap * tanh(x W^T / cap) (cap > 0) times mul_act(mul). */
+int xalm_cuda_moe_ffn_routed(float* out_pairs, int* idx, float* wgt, float* x_io, const float* h, const float* w_router, const float* w_gate,
+                             const float* w_up, const float* w_down, int T, int K, int E, int top, int ff, int n_groups, int keep_groups, int act,
+                             int w_bf16, int score_kind, int group_kind, int renormalise, float limit);
+int xalm_cuda_retention(float* out, float* state, const float* q, const float* k, const float* v, const float* gate, int T, int pos0, int H, int d, int dv,
+                        const float* decay, const float* freq, int rot_half, float k_scale, float eps);
+int xalm_cuda_latent_post(float* cq_out, float* cache_out, const float* proj, int T, int pos0, int q_rank, int kv_rank, int rot, const float* q_norm,
+                          const float* kv_norm, const float* freq, float eps, int ring, int cache_bf16);
+int xalm_cuda_latent_attend(float* out, const float* q, const float* cache, const float* gate, int T, int pos0, int H, int d, int r, int dv, int R, int ld,
+                            const float* uk, const float* uv, const float* freq, float scale, int n_splits, int cache_bf16, int w_bf16);
+int xalm_cuda_rows_act(float* out, const float* x, const float* w, int T, int N, int K, int act, float cap, const float* mul, int mul_act, int w_bf16);
+
 /* Tensor parallel plumbing (no reference analogue; north star).  Rank 0 makes an id, the host side ships it to
  * the other ranks (torch.distributed / MPI / a file), every rank calls comm_init before finalize. */
 #define XALM_COMM_ID_BYTES 128

@@ -47,16 +47,32 @@ def rotate(x, positions, freqs):
     return x
 
 
-def causal_softmax_attention(q, k, v, scale):
-    """q, k (T, H, n), v (T, H, dv): position i sees every j <= i; ordinary softmax; returns (T, H, dv)."""
+def causal_softmax_attention(q, k, v, scale, first_pos=0):
+    """q (T, H, n) for positions first_pos .. first_pos + T - 1; k (first_pos + T, H, n), v (first_pos + T, H, dv) for every position from 0:
+    position i sees every j <= i; ordinary softmax; returns (T, H, dv)."""
     T, H, _ = q.shape
     out = np.zeros((T, H, v.shape[-1]))
     for h in range(H):
-        for i in range(T):
-            s = (k[: i + 1, h] @ q[i, h]) * scale
+        for t in range(T):
+            i = first_pos + t
+            s = (k[: i + 1, h] @ q[t, h]) * scale
             p = np.exp(s - s.max())
-            out[i, h] = (p / p.sum()) @ v[: i + 1, h]
+            out[t, h] = (p / p.sum()) @ v[: i + 1, h]
     return out
+
+
+def attend_latents(q, c, k_rot, uk, uv, *, H, d, r, dv, scale, freqs, first_pos=0, gate=None):
+    """Attention of un-turned queries q (T, H (d + r)) at positions first_pos.. over latents c (n, R) and already turned shared keys k_rot (n, r):
+    keys and values are expanded per head; returns (T, H dv), times sigmoid(gate) when given."""
+    T, n = q.shape[0], c.shape[0]
+    q = f64(q).reshape(T, H, d + r)
+    k = (f64(c) @ f64(uk).T).reshape(n, H, d)
+    v = (f64(c) @ f64(uv).T).reshape(n, H, dv)
+    if r:
+        q = np.concatenate([q[:, :, :d], rotate(q[:, :, d:], np.arange(first_pos, first_pos + T), freqs)], axis=-1)
+        k = np.concatenate([k, np.repeat(f64(k_rot)[:, None, :], H, axis=1)], axis=-1)
+    o = causal_softmax_attention(q, k, v, scale, first_pos).reshape(T, H * dv)
+    return o if gate is None else o * sigmoid(gate)
 
 
 def latent(h, w_down, w_norm, rank, eps):
@@ -97,17 +113,14 @@ def latent_attention_gated(h, p, *, H, d, dv, R, Rq, scale, eps, c_from=None):
     return o @ f64(p["o"]).T, c
 
 
-def retention(h, p, *, H, d, dv, decay, rot_dims, base, eps, state=None, first_pos=0):
-    """S_t = decay_h S_{t-1} + k_t v_t^T, o_t = S_t^T q_t per head; o over its root mean square, times silu(W_g h), then W_o.
-    Returns the output and the state after the last token."""
-    T = h.shape[0]
-    h = f64(h)
-    pos = np.arange(first_pos, first_pos + T)
-    q = (h @ f64(p["q"]).T).reshape(T, H, d)
-    k = (h @ f64(p["k"]).T).reshape(T, H, d)
-    v = (h @ f64(p["v"]).T).reshape(T, H, dv)
-    if rot_dims:
-        freqs = rotary_frequencies(rot_dims, base)
+def retention_heads(q, k, v, *, decay, freqs=None, eps, state=None, first_pos=0, gate=None):
+    """q, k (T, H, d), v (T, H, dv): q and k turned, k times d^-1/2, then per head S_t = decay_h S_{t-1} + k_t v_t^T, o_t = S_t^T q_t from the
+    given state (zero when None); o over its root mean square, times silu(gate) when given.  Returns (T, H dv) and the state after the last token."""
+    T, H, d = q.shape
+    dv = v.shape[-1]
+    q, k, v = f64(q), f64(k), f64(v)
+    if freqs is not None and len(freqs):
+        pos = np.arange(first_pos, first_pos + T)
         q, k = rotate(q, pos, freqs), rotate(k, pos, freqs)
     k = k * d ** -0.5
     S = np.zeros((H, d, dv)) if state is None else f64(state).copy()
@@ -116,7 +129,19 @@ def retention(h, p, *, H, d, dv, decay, rot_dims, base, eps, state=None, first_p
         for hd in range(H):
             S[hd] = decay[hd] * S[hd] + np.outer(k[t, hd], v[t, hd])
             o[t, hd] = S[hd].T @ q[t, hd]
-    o = rms_norm(o, None, eps).reshape(T, H * dv) * silu(h @ f64(p["g"]).T)
+    o = rms_norm(o, None, eps).reshape(T, H * dv)
+    return (o if gate is None else o * silu(gate)), S
+
+
+def retention(h, p, *, H, d, dv, decay, rot_dims, base, eps, state=None, first_pos=0):
+    """The retention mixer on its input rows h; returns the output and the state after the last token."""
+    T = h.shape[0]
+    h = f64(h)
+    q = (h @ f64(p["q"]).T).reshape(T, H, d)
+    k = (h @ f64(p["k"]).T).reshape(T, H, d)
+    v = (h @ f64(p["v"]).T).reshape(T, H, dv)
+    o, S = retention_heads(q, k, v, decay=decay, freqs=rotary_frequencies(rot_dims, base) if rot_dims else None, eps=eps, state=state, first_pos=first_pos,
+                           gate=h @ f64(p["g"]).T)
     return o @ f64(p["o"]).T, S
 
 
@@ -208,3 +233,90 @@ def forward(cfg, w, tokens, return_layers=False):
         sums.append(x.copy())
     logits = softcap(rms_norm(x, w["final.norm"], eps) @ f64(w["head"]).T, cfg.get("logit_softcap", 0))
     return (logits, np.stack(sums)) if return_layers else logits
+
+
+# ---- small configurations and random weights for the tests -----------------------------------------------------------------------------
+def dense(ff):
+    return {"kind": "dense", "ff": ff}
+
+
+def moe(ff, experts, top, groups=0, keep=0, limit=1.5):
+    r = {"experts": experts, "top": top}
+    if groups:
+        r["groups"] = {"count": groups, "keep": keep}
+    return {"kind": "moe", "expert": {"ff": ff, "limit": limit}, "router": r}
+
+
+def latent_layer(heads, dim, rot_dim, vdim, kv_rank, q_rank, base=10000.0, scale=None, mlp=None):
+    mx = {"heads": heads, "dim": dim, "rot_dim": rot_dim, "vdim": vdim, "kv_rank": kv_rank, "q_rank": q_rank, "scale": scale or (dim + rot_dim) ** -0.5,
+          "rot": {"base": base, "dims": rot_dim}}
+    return {"type": "latent_attention", "mixer": mx, "mlp": mlp}
+
+
+def gated_latent_layer(heads, dim, vdim, kv_rank, q_rank, scale=None, kv_from=None, mlp=None):
+    mx = {"heads": heads, "dim": dim, "vdim": vdim, "kv_rank": kv_rank, "q_rank": q_rank, "scale": scale or dim ** -0.5}
+    if kv_from is not None:
+        mx["kv_from"] = kv_from
+    return {"type": "latent_attention_2", "mixer": mx, "mlp": mlp}
+
+
+def retention_layer(heads, dim, vdim, decay, rot_dims=0, base=10000.0, mlp=None):
+    mx = {"heads": heads, "dim": dim, "vdim": vdim, "decay": list(decay)}
+    if rot_dims:
+        mx["rot"] = {"base": base, "dims": rot_dims}
+    return {"type": "retention", "mixer": mx, "mlp": mlp}
+
+
+def make_config(vocab, width, layers, eps=1e-6, embed_scale=1.0, softcap=0.0):
+    c = {"architecture": "Duletar", "vocab": vocab, "width": width, "norm": {"eps": eps}, "embedding": {"scale": embed_scale}, "layers": layers}
+    if softcap:
+        c["logit_softcap"] = softcap
+    return c
+
+
+def bf16_round(a):
+    u = np.ascontiguousarray(a, dtype=np.float32).view(np.uint32)
+    return (((u + 0x7FFF + ((u >> 16) & 1)) >> 16) << 16).astype(np.uint32).view(np.float32)
+
+
+def random_weights(cfg, seed):
+    """name -> fp32 array, every value exactly representable in bfloat16 (so that both storage modes hold the same numbers)."""
+    rng = np.random.default_rng(seed)
+    W = cfg["width"]
+    w = {}
+
+    def mat(name, rows, cols, gain=1.0):
+        w[name] = bf16_round(rng.standard_normal((rows, cols)) * gain / math.sqrt(cols))
+
+    def vec(name, n):
+        w[name] = bf16_round(1.0 + 0.2 * rng.standard_normal(n))
+
+    w["embed"] = bf16_round(rng.standard_normal((cfg["vocab"], W)))
+    for li, L in enumerate(cfg["layers"]):
+        p, mx = f"l{li}.", L["mixer"]
+        H, d, dv = mx["heads"], mx["dim"], mx["vdim"]
+        vec(p + "norm1", W)
+        if L["type"] == "retention":
+            mat(p + "mix.q", H * d, W, 2.0); mat(p + "mix.k", H * d, W, 2.0); mat(p + "mix.v", H * dv, W); mat(p + "mix.g", H * dv, W)
+        else:
+            r, R, Rq = mx.get("rot_dim", 0), mx["kv_rank"], mx["q_rank"]
+            mat(p + "mix.dq", Rq, W); vec(p + "mix.dq.norm", Rq); mat(p + "mix.uq", H * (d + r), Rq, 2.0)
+            if "kv_from" not in mx:
+                mat(p + "mix.dkv", R + r, W); vec(p + "mix.dkv.norm", R)
+            mat(p + "mix.uk", H * d, R, 2.0); mat(p + "mix.uv", H * dv, R)
+            if L["type"] == "latent_attention_2":
+                mat(p + "mix.g", H * dv, W)
+        mat(p + "mix.o", W, H * dv)
+        ml = L.get("mlp")
+        if ml:
+            vec(p + "norm2", W)
+            if ml["kind"] == "dense":
+                mat(p + "mlp.up", ml["ff"], W); mat(p + "mlp.down", W, ml["ff"])
+            else:
+                ff = ml["expert"]["ff"]
+                for e in range(ml["router"]["experts"]):
+                    mat(f"{p}mlp.e{e}.gate", ff, W, 2.0); mat(f"{p}mlp.e{e}.up", ff, W, 2.0); mat(f"{p}mlp.e{e}.down", W, ff)
+                mat(p + "mlp.router", ml["router"]["experts"], W, 3.0)
+    vec("final.norm", W)
+    mat("head", cfg["vocab"], W, 3.0)
+    return w

@@ -96,6 +96,11 @@ SYMBOLS = {
     "xalm_cuda_qkv_post": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _i, _i, _i, C.c_float, _i, _i]),
     "xalm_cuda_delta_rule": (_i, [_vp] * 9 + [_i] * 6 + [_vp] * 6 + [C.c_float] * 3),
     "xalm_cuda_moe_ffn": (_i, [_vp] * 8 + [_i] * 9),
+    "xalm_cuda_moe_ffn_routed": (_i, [_vp] * 9 + [_i] * 12 + [C.c_float]),
+    "xalm_cuda_retention": (_i, [_vp] * 6 + [_i] * 5 + [_vp, _vp, _i, C.c_float, C.c_float]),
+    "xalm_cuda_latent_post": (_i, [_vp] * 3 + [_i] * 5 + [_vp] * 3 + [C.c_float, _i, _i]),
+    "xalm_cuda_latent_attend": (_i, [_vp] * 4 + [_i] * 8 + [_vp] * 3 + [C.c_float, _i, _i, _i]),
+    "xalm_cuda_rows_act": (_i, [_vp] * 3 + [_i] * 4 + [C.c_float, _vp, _i, _i]),
 }
 PRECISION_BF16, PRECISION_F32 = 0, 1            # enum xalm_precision
 
@@ -364,3 +369,57 @@ def moe_ffn(h, w_router, w_gate, w_up, w_down, top, n_groups=0, keep_groups=0, a
     check(lib().xalm_cuda_moe_ffn(_p(out), _p(idx), _p(wgt), _p(h), _p(w_router), _p(w_gate), _p(w_up), _p(w_down), T, K, E, top, ff, n_groups, keep_groups,
                                   act, int(w_bf16)))
     return idx, wgt, out
+
+
+def moe_ffn_routed(h, w_router, w_gate, w_up, w_down, top, n_groups=0, keep_groups=0, act=0, limit=float("inf"), score="softmax", group="max",
+                   renormalise=True, x=None, w_bf16=False):
+    """The router's variants.  Returns (idx, wgt, out (T, top, K), x + weighted sum or None)."""
+    h, w_router, w_gate, w_up, w_down = _f(h), _f(w_router), _f(w_gate), _f(w_up), _f(w_down)
+    T, K = h.shape
+    E, ff = w_gate.shape[0], w_gate.shape[1]
+    idx, wgt, out = np.empty((T, top), dtype=np.int32), np.empty((T, top), dtype=np.float32), np.empty((T, top, K), dtype=np.float32)
+    xo = None if x is None else np.array(x, dtype=np.float32, copy=True)
+    check(lib().xalm_cuda_moe_ffn_routed(_p(out), _p(idx), _p(wgt), _pn(xo), _p(h), _p(w_router), _p(w_gate), _p(w_up), _p(w_down), T, K, E, top, ff,
+                                         n_groups, keep_groups, act, int(w_bf16), {"sigmoid": 0, "softmax": 1}[score], {"top2": 0, "max": 1}[group],
+                                         int(renormalise), limit))
+    return idx, wgt, out, xo
+
+
+def retention(q, k, v, state, H, d, dv, decay, pos0=0, freq=None, gate=None, k_scale=None, eps=1e-6):
+    """Returns (out (T, H dv), new state); `state` (H, d, dv) is not modified."""
+    q, k, v, gate, decay, freq = _f(q), _f(k), _f(v), _f(gate), _f(decay), _f(freq)
+    st = np.array(state, dtype=np.float32, copy=True)
+    T = q.shape[0]
+    out = np.empty((T, H * dv), dtype=np.float32)
+    check(lib().xalm_cuda_retention(_p(out), _p(st), _p(q), _p(k), _p(v), _pn(gate), T, pos0, H, d, dv, _p(decay), _pn(freq),
+                                    0 if freq is None else freq.shape[0], d ** -0.5 if k_scale is None else k_scale, eps))
+    return out, st
+
+
+def latent_post(proj, pos0, q_rank, kv_rank, rot, q_norm, kv_norm, freq=None, eps=1e-6, ring=None, cache_bf16=False):
+    """Returns (normed query latent (T, q_rank), cache rows (ring, kv_rank + rot))."""
+    proj, q_norm, kv_norm, freq = _f(proj), _f(q_norm), _f(kv_norm), _f(freq)
+    T = proj.shape[0]
+    ring = pos0 + T if ring is None else ring
+    cq, cache = np.zeros((T, q_rank), dtype=np.float32), np.zeros((ring, kv_rank + rot), dtype=np.float32)
+    check(lib().xalm_cuda_latent_post(_p(cq), _p(cache), _p(proj), T, pos0, q_rank, kv_rank, rot, _pn(q_norm), _pn(kv_norm), _pn(freq), eps, ring,
+                                      int(cache_bf16)))
+    return cq, cache
+
+
+def latent_attend(q, cache, pos0, H, d, r, dv, R, uk, uv, scale, freq=None, gate=None, n_splits=0, cache_bf16=False, w_bf16=False):
+    q, cache, uk, uv, freq, gate = _f(q), _f(cache), _f(uk), _f(uv), _f(freq), _f(gate)
+    T = q.shape[0]
+    assert cache.shape[0] == pos0 + T
+    out = np.empty((T, H * dv), dtype=np.float32)
+    check(lib().xalm_cuda_latent_attend(_p(out), _p(q), _p(cache), _pn(gate), T, pos0, H, d, r, dv, R, cache.shape[1], _p(uk), _p(uv), _pn(freq), scale,
+                                        n_splits, int(cache_bf16), int(w_bf16)))
+    return out
+
+
+def rows_act(x, w, act=0, cap=0.0, mul=None, mul_act=2, w_bf16=False):
+    x, w, mul = _f(x), _f(w), _f(mul)
+    T, K = x.shape
+    out = np.empty((T, w.shape[0]), dtype=np.float32)
+    check(lib().xalm_cuda_rows_act(_p(out), _p(x), _p(w), T, w.shape[0], K, act, cap, _pn(mul), mul_act, int(w_bf16)))
+    return out

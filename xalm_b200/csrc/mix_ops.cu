@@ -12,6 +12,7 @@
 #include "family.h"
 #include "mix_ops.cuh"
 #include "delta_ops.cuh"
+#include "latent_ops.cuh"
 #include "moe_ops.cuh"
 
 using namespace xalm;
@@ -315,8 +316,11 @@ int xalm_cuda_delta_rule(float* out, float* state, float* conv_state, const floa
 	return XALM_OK;
 }
 
-int xalm_cuda_moe_ffn(float* out_pairs, int* idx, float* wgt, const float* h, const float* w_router, const float* w_gate, const float* w_up,
-                      const float* w_down, int T, int K, int E, int top, int ff, int n_groups, int keep_groups, int act, int w_bf16) {
+} // extern "C"
+
+static int moe_ffn_op(float* out_pairs, int* idx, float* wgt, const float* h, const float* w_router, const float* w_gate, const float* w_up,
+                      const float* w_down, int T, int K, int E, int top, int ff, int n_groups, int keep_groups, int act, int w_bf16, int score_kind,
+                      int group_kind, int renormalise, float limit, float* x_io) {
 	if (!out_pairs || !idx || !wgt || !h || !w_router || !w_gate || !w_up || !w_down || T <= 0 || K <= 0 || E <= 0 || top <= 0 || ff <= 0)
 		return set_error(XALM_ERR_INVALID, "moe_ffn: bad argument");
 	Pool pool;
@@ -340,6 +344,7 @@ int xalm_cuda_moe_ffn(float* out_pairs, int* idx, float* wgt, const float* h, co
 	ra.h = pool.put(h, (size_t) T * K); ra.ldh = K; ra.w = put_w(w_router, (size_t) E * K); ra.w_bf16 = w_bf16;
 	ra.E = E; ra.top = top; ra.K = K; ra.n_groups = n_groups; ra.keep_groups = keep_groups;
 	ra.idx = pool.raw<int>((size_t) P); ra.wgt = pool.raw<float>((size_t) P); ra.step = d_st;
+	ra.score_kind = score_kind; ra.group_kind = group_kind; ra.renormalise = renormalise; ra.renorm_eps = 1e-20f;
 	MoeSortArgs so = {ra.idx, top, E, d_st, pool.raw<int>((size_t) P), pool.raw<int>((size_t) 3 * max_tiles), pool.raw<int>(1), nullptr, nullptr};
 	MoeGemmArgs ga = {};
 	ga.A = ra.h; ga.lda = K; ga.a_div = top; ga.W = put_w(gu.data(), gu.size()); ga.N = 2 * ff; ga.K = K;
@@ -347,7 +352,7 @@ int xalm_cuda_moe_ffn(float* out_pairs, int* idx, float* wgt, const float* h, co
 	ga.idx = ra.idx; ga.step = d_st; ga.top = top;
 	float* hid = pool.raw<float>((size_t) P * ff);
 	float* outp = pool.raw<float>((size_t) P * K);
-	ga.e.kind = EPI_GLU; ga.e.glu_act = act; ga.e.out = hid; ga.e.ldo = ff; ga.e.limit = INFINITY;
+	ga.e.kind = EPI_GLU; ga.e.glu_act = act; ga.e.out = hid; ga.e.ldo = ff; ga.e.limit = limit;
 	void* d_down = put_w(w_down, (size_t) E * K * ff);
 	if (!d_st || !ra.h || !ra.w || !ra.idx || !ra.wgt || !so.sorted || !so.tiles || !so.n_tiles || !ga.W || !hid || !outp || !d_down)
 		return set_error(XALM_ERR_CUDA, "moe_ffn: device allocation failed");
@@ -359,10 +364,194 @@ int xalm_cuda_moe_ffn(float* out_pairs, int* idx, float* wgt, const float* h, co
 	ga.e = RowsEpi();
 	ga.e.kind = EPI_STORE; ga.e.out = outp; ga.e.ldo = K;
 	XALM_TRY(launch_moe_gemm(ga, w_bf16 != 0, P, E, nullptr));
+	float* d_x = pool.put(x_io, (size_t) T * K);
+	if (x_io) { // the residual stream takes the weighted sum of each token's rows
+		if (!d_x) return set_error(XALM_ERR_CUDA, "moe_ffn: device allocation failed");
+		MoeCombineArgs ca = {outp, K, top, K, ra.wgt, nullptr, d_x, d_x, d_st};
+		XALM_TRY(launch_moe_combine(ca, T, nullptr));
+	}
 	XALM_TRY(finish("moe_ffn"));
+	if (x_io) XALM_CUDA_CHECK(cudaMemcpy(x_io, d_x, (size_t) T * K * 4, cudaMemcpyDeviceToHost));
 	XALM_CUDA_CHECK(cudaMemcpy(out_pairs, outp, (size_t) P * K * 4, cudaMemcpyDeviceToHost));
 	XALM_CUDA_CHECK(cudaMemcpy(idx, ra.idx, (size_t) P * 4, cudaMemcpyDeviceToHost));
 	XALM_CUDA_CHECK(cudaMemcpy(wgt, ra.wgt, (size_t) P * 4, cudaMemcpyDeviceToHost));
+	return XALM_OK;
+}
+
+extern "C" {
+
+int xalm_cuda_moe_ffn(float* out_pairs, int* idx, float* wgt, const float* h, const float* w_router, const float* w_gate, const float* w_up,
+                      const float* w_down, int T, int K, int E, int top, int ff, int n_groups, int keep_groups, int act, int w_bf16) {
+	return moe_ffn_op(out_pairs, idx, wgt, h, w_router, w_gate, w_up, w_down, T, K, E, top, ff, n_groups, keep_groups, act, w_bf16, MOE_SCORE_SIGMOID,
+	                  MOE_GROUP_TOP2_SUM, 0, INFINITY, nullptr);
+}
+int xalm_cuda_moe_ffn_routed(float* out_pairs, int* idx, float* wgt, float* x_io, const float* h, const float* w_router, const float* w_gate,
+                             const float* w_up, const float* w_down, int T, int K, int E, int top, int ff, int n_groups, int keep_groups, int act,
+                             int w_bf16, int score_kind, int group_kind, int renormalise, float limit) {
+	return moe_ffn_op(out_pairs, idx, wgt, h, w_router, w_gate, w_up, w_down, T, K, E, top, ff, n_groups, keep_groups, act, w_bf16, score_kind, group_kind,
+	                  renormalise, limit, x_io);
+}
+
+int xalm_cuda_retention(float* out, float* state, const float* q, const float* k, const float* v, const float* gate, int T, int pos0, int H, int d, int dv,
+                        const float* decay, const float* freq, int rot_half, float k_scale, float eps) {
+	if (!out || !state || !q || !k || !v || !decay || T <= 0 || pos0 < 0 || H <= 0 || d <= 0 || dv <= 0 || rot_half < 0 || 2 * rot_half > d || (rot_half && !freq))
+		return set_error(XALM_ERR_INVALID, "retention: bad argument");
+	const size_t smem = hgrn2_smem_bytes(d, dv);
+	if (!hgrn2_cols_ok(d, dv, T) && (smem > 200 * 1024 || dv > 1024)) return set_error(XALM_ERR_UNSUPPORTED, "retention: a head's state needs %zu bytes of shared memory", smem);
+	Pool pool;
+	const int ld = 2 * H * d + 2 * H * dv; // q | k | v | gate, as the family's input projection leaves them
+	std::vector<float> proj((size_t) T * ld, 0.f);
+	for (int t = 0; t < T; t++) {
+		memcpy(&proj[(size_t) t * ld], q + (size_t) t * H * d, (size_t) H * d * 4);
+		memcpy(&proj[(size_t) t * ld + H * d], k + (size_t) t * H * d, (size_t) H * d * 4);
+		memcpy(&proj[(size_t) t * ld + 2 * H * d], v + (size_t) t * H * dv, (size_t) H * dv * 4);
+		if (gate) memcpy(&proj[(size_t) t * ld + 2 * H * d + H * dv], gate + (size_t) t * H * dv, (size_t) H * dv * 4);
+	}
+	const SeqStep st = {pos0, T};
+	float* d_proj = pool.put(proj.data(), proj.size());
+	const SeqStep* d_st = pool.put(&st, 1);
+	const float* d_freq = pool.put(freq, (size_t) rot_half);
+	Hgrn2Args a = {};
+	a.proj = d_proj; a.ld = ld; a.q_off = 0; a.k_off = H * d; a.v_off = 2 * H * d;
+	a.H = H; a.d = d; a.dv = dv;
+	a.decay = pool.put(decay, (size_t) H); a.k_scale = k_scale; a.norm_plain = 1; a.eps = eps;
+	if (gate) { a.gate = d_proj; a.ldg = ld; a.g_off = 2 * H * d + H * dv; }
+	a.state = pool.put(state, (size_t) H * d * dv);
+	a.step = d_st;
+	a.out = pool.raw<float>((size_t) T * H * dv);
+	a.max_rows = T;
+	if (!d_proj || !d_st || !a.decay || !a.state || !a.out || (rot_half && !d_freq)) return set_error(XALM_ERR_CUDA, "retention: device allocation failed");
+	if (rot_half) {
+		RopeHeadsArgs ra = {};
+		ra.src = d_proj; ra.dst = d_proj; ra.lds = ra.ldd = ld; ra.src_stride = ra.dst_stride = d;
+		ra.heads = 2 * H; ra.n = d; ra.rot_half = rot_half; ra.freq = d_freq; ra.step = d_st;
+		XALM_TRY(launch_rope_heads(ra, T, nullptr));
+	}
+	XALM_TRY(hgrn2_prepare(d, dv));
+	XALM_TRY(launch_hgrn2(a, nullptr));
+	XALM_TRY(finish("retention"));
+	XALM_CUDA_CHECK(cudaMemcpy(out, a.out, (size_t) T * H * dv * 4, cudaMemcpyDeviceToHost));
+	XALM_CUDA_CHECK(cudaMemcpy(state, a.state, (size_t) H * d * dv * 4, cudaMemcpyDeviceToHost));
+	return XALM_OK;
+}
+
+int xalm_cuda_latent_post(float* cq_out, float* cache_out, const float* proj, int T, int pos0, int q_rank, int kv_rank, int rot, const float* q_norm,
+                          const float* kv_norm, const float* freq, float eps, int ring, int cache_bf16) {
+	if (!proj || T <= 0 || pos0 < 0 || q_rank < 0 || kv_rank < 0 || rot < 0 || rot % 2 || ring <= 0 || (q_rank && (!cq_out || !q_norm)) ||
+	    (kv_rank && (!cache_out || !kv_norm)) || (rot && !freq))
+		return set_error(XALM_ERR_INVALID, "latent_post: bad argument");
+	Pool pool;
+	const int ld = q_rank + kv_rank + rot, cl = kv_rank + rot;
+	const SeqStep st = {pos0, T};
+	LatentPostArgs a = {};
+	a.proj = pool.put(proj, (size_t) T * ld); a.ld = ld;
+	a.q_off = 0; a.q_rank = q_rank; a.q_norm = pool.put(q_norm, (size_t) q_rank); a.cq = pool.raw<float>((size_t) T * std::max(1, q_rank)); a.ldc = q_rank;
+	a.kv_off = q_rank; a.kv_rank = kv_rank; a.rot = kv_rank ? rot : 0; a.kv_norm = pool.put(kv_norm, (size_t) kv_rank); a.freq = pool.put(freq, (size_t) rot / 2);
+	a.eps = eps; a.cache_f32 = !cache_bf16; a.ring = ring;
+	a.cache = pool.raw<float>((size_t) ring * std::max(1, cl));
+	a.step = pool.put(&st, 1);
+	if (!a.proj || !a.cq || !a.cache || !a.step) return set_error(XALM_ERR_CUDA, "latent_post: device allocation failed");
+	XALM_TRY(launch_latent_post(a, T, nullptr));
+	XALM_TRY(finish("latent_post"));
+	if (q_rank) XALM_CUDA_CHECK(cudaMemcpy(cq_out, a.cq, (size_t) T * q_rank * 4, cudaMemcpyDeviceToHost));
+	if (kv_rank) {
+		if (!cache_bf16) XALM_CUDA_CHECK(cudaMemcpy(cache_out, a.cache, (size_t) ring * cl * 4, cudaMemcpyDeviceToHost));
+		else {
+			std::vector<uint16_t> hb((size_t) ring * cl);
+			XALM_CUDA_CHECK(cudaMemcpy(hb.data(), a.cache, hb.size() * 2, cudaMemcpyDeviceToHost));
+			for (size_t i = 0; i < hb.size(); i++) {
+				const uint32_t u = (uint32_t) hb[i] << 16;
+				memcpy(&cache_out[i], &u, 4);
+			}
+		}
+	}
+	return XALM_OK;
+}
+
+int xalm_cuda_latent_attend(float* out, const float* q, const float* cache, const float* gate, int T, int pos0, int H, int d, int r, int dv, int R, int ld,
+                            const float* uk, const float* uv, const float* freq, float scale, int n_splits, int cache_bf16, int w_bf16) {
+	if (!out || !q || !cache || !uk || !uv || T <= 0 || pos0 < 0 || H <= 0 || d <= 0 || r < 0 || r % 2 || dv <= 0 || R <= 0 || ld < R + r || n_splits < 0 || (r && !freq))
+		return set_error(XALM_ERR_INVALID, "latent_attend: bad argument");
+	const int n = pos0 + T, da = R + r;
+	if (!swa_pick_tq(H, 1, da, R, T) && swa_smem_bytes(H, da, R) > 200 * 1024) return set_error(XALM_ERR_UNSUPPORTED, "latent_attend: heads need too much shared memory");
+	Pool pool;
+	auto put_w = [&](const float* src, size_t cnt) -> void* {
+		if (!w_bf16) return pool.put(src, cnt);
+		std::vector<uint16_t> wb(cnt);
+		for (size_t i = 0; i < cnt; i++) wb[i] = bf16_bits(src[i]);
+		return pool.put(wb.data(), cnt);
+	};
+	std::vector<float> ukT((size_t) H * R * d); // uk (H d, R) as H matrices (R, d)
+	for (int h = 0; h < H; h++)
+		for (int i = 0; i < d; i++)
+			for (int j = 0; j < R; j++) ukT[((size_t) h * R + j) * d + i] = uk[((size_t) h * d + i) * R + j];
+	void* d_cache;
+	if (cache_bf16) {
+		std::vector<uint16_t> cb((size_t) n * ld);
+		for (size_t i = 0; i < cb.size(); i++) cb[i] = bf16_bits(cache[i]);
+		d_cache = pool.put(cb.data(), cb.size());
+	} else d_cache = pool.put(cache, (size_t) n * ld);
+	const SeqStep st = {pos0, T};
+	const SeqStep* d_st = pool.put(&st, 1);
+	const float* d_q = pool.put(q, (size_t) T * H * (d + r));
+	const float* d_gate = pool.put(gate, (size_t) T * H * dv);
+	const float* d_freq = pool.put(freq, (size_t) r / 2);
+	void *d_ukT = put_w(ukT.data(), ukT.size()), *d_uv = put_w(uv, (size_t) H * dv * R);
+	float *qabs = pool.raw<float>((size_t) T * H * da), *olat = pool.raw<float>((size_t) T * H * R), *d_out = pool.raw<float>((size_t) T * H * dv);
+	if (!d_cache || !d_st || !d_q || !d_ukT || !d_uv || !qabs || !olat || !d_out || (gate && !d_gate) || (r && !d_freq))
+		return set_error(XALM_ERR_CUDA, "latent_attend: device allocation failed");
+	RowsEpi eb;
+	eb.kind = EPI_STORE; eb.out = qabs; eb.ldo = H * da; eb.batch_a = d + r; eb.batch_w = (size_t) R * d; eb.batch_o = da;
+	XALM_TRY(launch_rows(d_q, H * (d + r), d_ukT, w_bf16 != 0, T, R, d, eb, nullptr, H));
+	if (r) {
+		RopeHeadsArgs ra = {};
+		ra.src = d_q; ra.lds = H * (d + r); ra.src_off = d; ra.src_stride = d + r;
+		ra.dst = qabs; ra.ldd = H * da; ra.dst_off = R; ra.dst_stride = da;
+		ra.heads = H; ra.n = r; ra.rot_half = r / 2; ra.freq = d_freq; ra.step = d_st;
+		XALM_TRY(launch_rope_heads(ra, T, nullptr));
+	}
+	SwaArgs sa = {};
+	sa.q = qabs; sa.ldq = H * da;
+	sa.kc = d_cache; sa.vc = d_cache; sa.ldk = ld; sa.ldv = ld; sa.ring = n;
+	sa.H = H; sa.G = 1; sa.d = da; sa.dv = R; sa.window = 0x7fffffff; sa.scale = scale;
+	sa.step = d_st; sa.out = olat;
+	sa.n_splits = n_splits;
+	const int cap = std::max(4 * 64, 4 * T);
+	sa.part_cap = n_splits ? T * n_splits : cap;
+	sa.part_o = pool.raw<float>((size_t) sa.part_cap * H * R);
+	sa.part_ml = pool.raw<float>((size_t) sa.part_cap * H * 2);
+	sa.tickets = pool.raw<unsigned>((size_t) T);
+	if (!sa.part_o || !sa.part_ml || !sa.tickets) return set_error(XALM_ERR_CUDA, "latent_attend: device allocation failed");
+	XALM_TRY(launch_swa(sa, T, cache_bf16 == 0, nullptr));
+	RowsEpi ev;
+	ev.kind = EPI_STORE; ev.out = d_out; ev.ldo = H * dv; ev.batch_a = R; ev.batch_w = (size_t) dv * R; ev.batch_o = dv;
+	if (gate) { ev.mul = d_gate; ev.ldm = H * dv; ev.mul_act = ACT_SIGMOID; }
+	XALM_TRY(launch_rows(olat, H * R, d_uv, w_bf16 != 0, T, dv, R, ev, nullptr, H));
+	XALM_TRY(finish("latent_attend"));
+	XALM_CUDA_CHECK(cudaMemcpy(out, d_out, (size_t) T * H * dv * 4, cudaMemcpyDeviceToHost));
+	return XALM_OK;
+}
+
+int xalm_cuda_rows_act(float* out, const float* x, const float* w, int T, int N, int K, int act, float cap, const float* mul, int mul_act, int w_bf16) {
+	if (!out || !x || !w || T <= 0 || N <= 0 || K <= 0) return set_error(XALM_ERR_INVALID, "rows_act: bad argument");
+	Pool pool;
+	void* d_w;
+	if (w_bf16) {
+		std::vector<uint16_t> wb((size_t) N * K);
+		for (size_t i = 0; i < wb.size(); i++) wb[i] = bf16_bits(w[i]);
+		d_w = pool.put(wb.data(), wb.size());
+	} else d_w = pool.put(w, (size_t) N * K);
+	const float* d_x = pool.put(x, (size_t) T * K);
+	const float* d_mul = pool.put(mul, (size_t) T * N);
+	float* d_out = pool.raw<float>((size_t) T * N);
+	if (!d_w || !d_x || !d_out || (mul && !d_mul)) return set_error(XALM_ERR_CUDA, "rows_act: device allocation failed");
+	RowsEpi e;
+	e.out = d_out; e.ldo = N;
+	if (act != ACT_NONE) { e.kind = EPI_ACT; e.act = act; }
+	else { e.kind = EPI_STORE; e.cap = cap; e.mul = d_mul; e.ldm = N; e.mul_act = mul_act; }
+	XALM_TRY(launch_rows(d_x, K, d_w, w_bf16 != 0, T, N, K, e, nullptr));
+	XALM_TRY(finish("rows_act"));
+	XALM_CUDA_CHECK(cudaMemcpy(out, d_out, (size_t) T * N * 4, cudaMemcpyDeviceToHost));
 	return XALM_OK;
 }
 
