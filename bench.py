@@ -477,6 +477,57 @@ def build_bolovik(z: dict, seed: int, max_tokens: int, stream):
     return m
 
 
+def duletar_config(z: dict) -> dict:
+    """Layers cycle through: retention with a dense feed-forward; rotary latent attention with a mixture of 16 clamped experts of ff / 4 of which
+    4 are chosen (as many active feed-forward weights as the dense layer); gated latent attention reading the layer before's latents, same
+    mixture; retention with the mixture.  Latents: keys/values width / 4 within [256, 512], queries 3 width / 8; heads of 128 + 64 rotated."""
+    W = z["width"]
+    R, Rq, d, r = min(512, max(256, W // 4)), 3 * W // 8, z["head_dim"], z["head_dim"] // 2
+    ret = {"heads": 2 * z["r_heads"], "dim": z["r_dim"], "vdim": z["r_vdim"], "decay": [1.0 - 2.0 ** (-5 - 0.25 * h) for h in range(2 * z["r_heads"])],
+           "rot": {"base": 10000.0, "dims": z["r_dim"]}}
+    lat = {"heads": z["heads"], "dim": d, "rot_dim": r, "vdim": d, "kv_rank": R, "q_rank": Rq, "scale": (d + r) ** -0.5, "rot": {"base": 10000.0, "dims": r}}
+    gated = {"heads": z["heads"], "dim": d, "vdim": d, "kv_rank": R, "q_rank": Rq, "scale": d ** -0.5}
+    moe = {"kind": "moe", "expert": {"ff": z["ff"] // 4, "limit": 7.0}, "router": {"experts": 16, "top": 4, "groups": {"count": 4, "keep": 2}}}
+    layers = []
+    for i in range(z["layers"]):
+        k = i % 4
+        if k == 0: layers.append({"type": "retention", "mixer": ret, "mlp": {"kind": "dense", "ff": z["ff"]}})
+        elif k == 1: layers.append({"type": "latent_attention", "mixer": lat, "mlp": moe})
+        elif k == 2: layers.append({"type": "latent_attention_2", "mixer": dict(gated, kv_from=i - 1), "mlp": moe})
+        else: layers.append({"type": "retention", "mixer": ret, "mlp": moe})
+    return {"architecture": "Duletar", "vocab": z["vocab"], "width": W, "norm": {"eps": 1e-6}, "embedding": {"scale": float(W) ** 0.5},
+            "logit_softcap": 30.0, "layers": layers}
+
+
+def build_duletar(z: dict, seed: int, max_tokens: int, stream):
+    """Random bf16 weights, uploaded tensor by tensor as the backend names them."""
+    import ctypes as C
+    import json
+    from xalm_b200 import capi, safetensors_io as ST, types as T
+    from xalm_b200.model import Model
+    m = Model._from_json_text(json.dumps(duletar_config(z)), {})
+    L = capi.lib()
+    h = C.c_void_p()
+    capi.check(L.xalm_cuda_create_json(m.config["json"].encode(), 0, max_tokens, capi.PRECISION_BF16, C.byref(h)))
+    m._h = h
+    capi.check(L.xalm_cuda_set_stream(h, C.c_void_p(stream)))
+    rng = np.random.default_rng(seed)
+    for name, shape in m.expected_tensors().items():
+        leaf = name.split(".")[-1]
+        if name == "embed":
+            a = rng.standard_normal(shape, dtype=np.float32) * np.float32(1.0 / np.sqrt(shape[1]))   # times sqrt(width) in the model: rows of order one
+        elif len(shape) == 2:
+            a = rng.standard_normal(shape, dtype=np.float32) * np.float32((2.0 if leaf == "router" else 1.0) / np.sqrt(shape[1]))
+        elif leaf in ("norm1", "norm2"):
+            a = 0.3 + 0.05 * rng.standard_normal(shape, dtype=np.float32)
+        else:
+            a = 1.0 + 0.1 * rng.standard_normal(shape, dtype=np.float32)
+        m.upload(name, T.BF16, shape, ST.f32_to_bf16_bits(a).view(np.uint8).reshape(-1))
+    capi.check(L.xalm_cuda_finalize(h))
+    m.config["vocab_size"] = z["vocab"]
+    return m
+
+
 def run_family_workload(args, fams=("nabalix", "llama")):
     """Prefill and one-token-step throughput of config.json families beside one another and beside the Llama family at equal layer sizes
     (bf16 weights, random), device-timed with CUDA events on the launching stream.  One JSON line; `value` is the first family's decode rate
@@ -501,7 +552,7 @@ def run_family_workload(args, fams=("nabalix", "llama")):
             for fam in fams:
                 if fam != "llama":
                     capi.tune("seq_chunk", args.seq_chunk)  # positions per pass of a prompt (the Llama arm takes the prompt in one pass)
-                    m = (build_nabalix if fam == "nabalix" else build_bolovik)(z, args.seed, ctx, stream.cuda_stream)
+                    m = {"nabalix": build_nabalix, "bolovik": build_bolovik, "duletar": build_duletar}[fam](z, args.seed, ctx, stream.cuda_stream)
                 else:
                     m, _ = build_model_streaming(llama_full, llama_cfg, T.BF16, args.seed, False, stream=stream.cuda_stream)
                     capi.tune("prefill_split", 1)        # plain fp16 operands, the counterpart of the one-plane path
@@ -562,11 +613,13 @@ def main():
     ap.add_argument("--past-window", action="store_true",
                     help="also time steps at positions >= ctx: the KV ring is full (kv_len = ctx), 2 attention sinks active (infer.cpp:608-613)")
     ap.add_argument("--no-prefill", action="store_true", help="skip the perplexity-mode summary appended to the decode line at N=1")
-    ap.add_argument("--workload", default="decode", choices=["decode", "perplexity", "families", "bolovik"],
+    ap.add_argument("--workload", default="decode", choices=["decode", "perplexity", "families", "bolovik", "duletar"],
                     help="decode = BASELINE config[1] (the headline metric); perplexity = config[2]: batched prefill of a 4k-token input; "
                          "families = prefill and one-token-step throughput of the Nabalix family beside the Llama family at equal layer sizes; "
-                         "bolovik = the same for the Bolovik family beside the Nabalix and Llama families")
-    ap.add_argument("--arms", default="bolovik,nabalix,llama", help="bolovik workload: which families run, the first one is the headline")
+                         "bolovik = the same for the Bolovik family beside the Nabalix and Llama families; "
+                         "duletar = the same for the Duletar family beside the Bolovik family")
+    ap.add_argument("--arms", default="", help="bolovik / duletar workloads: which families run, the first one is the headline "
+                                               "(default bolovik,nabalix,llama / duletar,bolovik)")
     ap.add_argument("--seq-chunk", type=int, default=1024, help="families workload: positions per pass of a Nabalix prompt")
     ap.add_argument("--sizes", default="w1024,w2048,w4096", help="families workload: which of " + ",".join(FAMILY_SIZES))
     ap.add_argument("--tokens", type=int, default=4096, help="perplexity workload: tokens per step")
@@ -577,7 +630,9 @@ def main():
     if args.workload == "perplexity":
         run_perplexity_workload(args)
         return
-    if args.workload in ("families", "bolovik"):
+    if args.workload in ("families", "bolovik", "duletar"):
+        if not args.arms:
+            args.arms = "duletar,bolovik" if args.workload == "duletar" else "bolovik,nabalix,llama"
         if args.steps == 256:
             args.steps = 64
         if args.tokens == 4096:
