@@ -70,7 +70,8 @@ def latent_case(rng, n, H, d, r, dv, R, extra=0):
     return c, k_rot, rows, uk, uv
 
 
-@pytest.mark.parametrize("H,d,r,dv,R", [(4, 8, 6, 12, 16), (1, 5, 0, 7, 12), (3, 16, 2, 4, 40), (2, 64, 32, 48, 72), (6, 3, 4, 5, 9)])
+@pytest.mark.parametrize("H,d,r,dv,R", [(4, 8, 6, 12, 16), (1, 5, 0, 7, 12), (3, 16, 2, 4, 40), (2, 64, 32, 48, 72), (6, 3, 4, 5, 9),
+                                       (32, 4, 2, 3, 560)])   # the last: 32 heads over a latent of 560 do not fit one CTA; the heads run in two launches
 @pytest.mark.parametrize("T,pos0", [(1, 0), (1, 200), (3, 97), (40, 0), (37, 60)])
 def test_latent_attention_over_rows(H, d, r, dv, R, T, pos0):
     """Queries mapped into the latent, one shared key/value head read in place, values expanded afterwards: the same numbers as keys and

@@ -530,7 +530,7 @@ int finalize(SeqModel* sm) {
 	XALM_TRY(dev_alloc(m, &m->ffh, C * max_ff));
 	XALM_TRY(dev_alloc(m, &m->part_o, (size_t) m->part_cap * max_olat));
 	XALM_TRY(dev_alloc(m, &m->part_ml, (size_t) m->part_cap * 2 * max_h));
-	XALM_TRY(dev_alloc(m, &m->tickets, C, true));
+	XALM_TRY(dev_alloc(m, &m->tickets, 8 * C, true)); // the heads of a layer may run in up to 8 launches, each with counters of its own
 	if (max_pairs) {
 		XALM_TRY(dev_alloc(m, &m->moe_idx, max_pairs, true));
 		XALM_TRY(dev_alloc(m, &m->moe_wgt, max_pairs, true));

@@ -520,7 +520,7 @@ int xalm_cuda_latent_attend(float* out, const float* q, const float* cache, cons
 	sa.part_cap = n_splits ? T * n_splits : cap;
 	sa.part_o = pool.raw<float>((size_t) sa.part_cap * H * R);
 	sa.part_ml = pool.raw<float>((size_t) sa.part_cap * H * 2);
-	sa.tickets = pool.raw<unsigned>((size_t) T);
+	sa.tickets = pool.raw<unsigned>((size_t) 8 * T);
 	if (!sa.part_o || !sa.part_ml || !sa.tickets) return set_error(XALM_ERR_CUDA, "latent_attend: device allocation failed");
 	XALM_TRY(launch_swa(sa, T, cache_bf16 == 0, nullptr));
 	RowsEpi ev;

@@ -435,7 +435,9 @@ struct SwaArgs {
 	const float* r2;
 	const float* talk; // (H, H) score_h <- sum_g talk[h, g] score_g; NULL: none
 	const SeqStep* step;
-	float* out;        // (T, H * dv)
+	float* out;        // (T, ldo): head h at columns h * dv
+	int ldo;           // 0: H * dv.  The launcher runs the heads of a single-group attention in several launches when all of them do not fit one
+	                   // CTA's shared memory: each launch sees its share of the heads as H and the full row as ldo
 	int n_splits;      // > 1: partial results to part_*; swa_merge_kernel finishes.  0: the launcher chooses (part_cap bounds it)
 	int part_cap;      // (row, split) pairs part_o / part_ml have room for (only read when n_splits == 0)
 	int tq;            // queries per CTA of the tiled kernel (set by the launcher)
@@ -501,7 +503,7 @@ __device__ __forceinline__ void swa_merge_one(const SwaArgs& a, int t, int hc) {
 	}
 	float o = num / den;
 	if (a.gate) o *= sigmoidf_(a.gate[(size_t) t * a.ldg + a.g_off + hc]);
-	a.out[(size_t) t * (H * dv) + hc] = o;
+	a.out[(size_t) t * (a.ldo ? a.ldo : H * dv) + hc] = o;
 }
 __device__ __forceinline__ void swa_merge_rows(const SwaArgs& a, int t_first, int rows, int tid, int nth) {
 	const int hdv = a.H * a.dv;
@@ -558,8 +560,11 @@ __global__ void __launch_bounds__(256) swa_attn_kernel(SwaArgs a) {
 	const int jb = sp * per, je = min(nk, jb + per); // virtual key indices
 	// staged rows: Ks[jj][G d], Vs[jj][G dv] in the cache's element type
 	const bool staged = a.stage_off > 0;
+	// one key/value head whose values are the first dv entries of the key rows (a latent cache): the staged key rows serve as values too
+	const bool v_in_k = a.vc == a.kc && ldv == ldk && G == 1 && dv <= d;
+	const int vs_ld = v_in_k ? G * d : G * dv;
 	CT* Ks = reinterpret_cast<CT*>(sm + a.stage_off);
-	CT* Vs = Ks + (size_t) SWA_KB * G * d;
+	CT* Vs = v_in_k ? Ks : Ks + (size_t) SWA_KB * G * d;
 	auto stage = [&](int j0, int nb) {
 		constexpr int EPC = 16 / (int) sizeof(CT); // elements per 16-byte copy
 		const int kch = G * d / EPC, vch = G * dv / EPC;
@@ -568,7 +573,7 @@ __global__ void __launch_bounds__(256) swa_attn_kernel(SwaArgs a) {
 			const unsigned dst = (unsigned) __cvta_generic_to_shared(Ks + (size_t) jj * (G * d) + c);
 			asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(kc + (size_t) km.slot(j0 + jj) * ldk + c) : "memory");
 		}
-		for (int x = tid; x < nb * vch; x += nth) {
+		for (int x = tid; x < (v_in_k ? 0 : nb * vch); x += nth) {
 			const int jj = x / vch, c = (x % vch) * EPC;
 			const unsigned dst = (unsigned) __cvta_generic_to_shared(Vs + (size_t) jj * (G * dv) + c);
 			asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(vc + (size_t) km.slot(j0 + jj) * ldv + c) : "memory");
@@ -696,7 +701,7 @@ __global__ void __launch_bounds__(256) swa_attn_kernel(SwaArgs a) {
 				for (int jb8 = 0; jb8 < nb; jb8 += 8) { // eight loads in flight
 					float v[8];
 #pragma unroll
-					for (int e8 = 0; e8 < 8; e8++) v[e8] = jb8 + e8 < nb ? ldf(vcol + (staged ? (size_t) (jb8 + e8) * (G * dv) : (size_t) km.slot(j0 + jb8 + e8) * ldv)) : 0.f;
+					for (int e8 = 0; e8 < 8; e8++) v[e8] = jb8 + e8 < nb ? ldf(vcol + (staged ? (size_t) (jb8 + e8) * vs_ld : (size_t) km.slot(j0 + jb8 + e8) * ldv)) : 0.f;
 #pragma unroll
 					for (int e8 = 0; e8 < 8; e8++)
 #pragma unroll
@@ -714,7 +719,7 @@ __global__ void __launch_bounds__(256) swa_attn_kernel(SwaArgs a) {
 		for (int x = tid; x < H * dv; x += nth) {
 			float o = O[x] / lrun[x / dv];
 			if (a.gate) o *= sigmoidf_(a.gate[(size_t) t * a.ldg + a.g_off + x]);
-			a.out[(size_t) t * (H * dv) + x] = o;
+			a.out[(size_t) t * (a.ldo ? a.ldo : H * dv) + x] = o;
 		}
 	} else {
 		float* po = a.part_o + ((size_t) t * a.n_splits + sp) * (H * dv);
@@ -726,7 +731,7 @@ __global__ void __launch_bounds__(256) swa_attn_kernel(SwaArgs a) {
 
 // float offset of the staged rows behind the kernel's own arrays (16-byte aligned), and the bytes they take
 inline size_t swa_stage_off(int H, int d, int dv) { return ((size_t) H * d + 2 * (size_t) H * SWA_KB + (size_t) H * H + 3 * (size_t) H + (size_t) H * dv + 3) & ~(size_t) 3; }
-inline size_t swa_stage_bytes(int G, int d, int dv, bool cache_f32) { return (size_t) SWA_KB * G * (d + dv) * (cache_f32 ? 4 : 2); }
+inline size_t swa_stage_bytes(int G, int d, int dv, bool cache_f32, bool v_in_k = false) { return (size_t) SWA_KB * G * (d + (v_in_k ? 0 : dv)) * (cache_f32 ? 4 : 2); }
 inline size_t swa_smem_bytes(int H, int d, int dv) { return sizeof(float) * ((size_t) H * d + 2 * (size_t) H * SWA_KB + (size_t) H * H + 3 * (size_t) H + (size_t) H * dv); }
 
 
@@ -1004,7 +1009,7 @@ __global__ void __launch_bounds__(256) swa_tile_kernel(SwaArgs a) {
 		if (a.n_splits == 1) {
 			float o = acc / lrun[row];
 			if (a.gate) o *= sigmoidf_(a.gate[(size_t) t * a.ldg + a.g_off + h * dv + c]);
-			a.out[(size_t) t * (H * dv) + h * dv + c] = o;
+			a.out[(size_t) t * (a.ldo ? a.ldo : H * dv) + h * dv + c] = o;
 		} else a.part_o[((size_t) t * a.n_splits + sp) * (H * dv) + h * dv + c] = acc;
 	}
 	if (a.n_splits > 1)
@@ -1685,6 +1690,32 @@ static inline int swa_pick_tq(int H, int G, int d, int dv, int rows) {
 // rows: tokens of the step; cache_f32: element type of the ring.  With n_splits > 1 the merge kernel follows.  Returns the number of
 // launches through *launches (1 or 2) when it is given.
 static inline int launch_swa(SwaArgs a, int rows, bool cache_f32, cudaStream_t s, int* launches = nullptr) {
+	// One key/value group, no score mixing, more than a few rows, and all heads together do not fit a CTA's shared memory in the tiled kernel
+	// (many heads over a wide latent): the heads run in 2, 4 or 8 launches, each a smaller attention of its own on its share of the query
+	// and output columns, with its own slice of the partial buffers and ticket counters.
+	if (a.G == 1 && !a.talk && rows > 4 && !a.ldo && !swa_pick_tq(a.H, 1, a.d, a.dv, rows)) {
+		for (int nz = 2; nz <= 8; nz *= 2) {
+			if (a.H % nz || !swa_pick_tq(a.H / nz, 1, a.d, a.dv, rows)) continue;
+			const int Hc = a.H / nz;
+			const int cap = a.n_splits > 0 ? rows * a.n_splits : a.part_cap;
+			if (launches) *launches = 0;
+			for (int z = 0; z < nz; z++) {
+				SwaArgs b = a;
+				b.H = Hc;
+				b.ldo = a.H * a.dv;
+				b.q_off = a.q_off + z * Hc * a.d;
+				b.g_off = a.g_off + z * Hc * a.dv;
+				b.out = a.out + (size_t) z * Hc * a.dv;
+				if (a.part_o) b.part_o = a.part_o + (size_t) z * cap * Hc * a.dv;
+				if (a.part_ml) b.part_ml = a.part_ml + (size_t) z * cap * Hc * 2;
+				if (a.tickets) b.tickets = a.tickets + (size_t) z * rows;
+				int one = 1;
+				XALM_TRY(launch_swa(b, rows, cache_f32, s, &one));
+				if (launches) *launches += one;
+			}
+			return XALM_OK;
+		}
+	}
 	const int tq = swa_pick_tq(a.H, a.G, a.d, a.dv, rows);
 	if (a.n_splits <= 0) { // enough CTAs for two waves, at least two key blocks each
 		const int qblocks = tq ? (rows + tq - 1) / tq : rows;
@@ -1707,7 +1738,8 @@ static inline int launch_swa(SwaArgs a, int rows, bool cache_f32, cudaStream_t s
 		else swa_tile_kernel<__nv_bfloat16><<<grid, 256, smem, s>>>(a);
 	} else {
 		size_t smem = swa_smem_bytes(a.H, a.d, a.dv);
-		const size_t staged = swa_stage_off(a.H, a.d, a.dv) * 4 + swa_stage_bytes(a.G, a.d, a.dv, cache_f32);
+		const bool v_in_k = a.vc == a.kc && (a.ldv ? a.ldv : a.G * a.dv) == (a.ldk ? a.ldk : a.G * a.d) && a.G == 1 && a.dv <= a.d; // as the kernel decides
+		const size_t staged = swa_stage_off(a.H, a.d, a.dv) * 4 + swa_stage_bytes(a.G, a.d, a.dv, cache_f32, v_in_k);
 		a.stage_off = 0;
 		const bool rows16 = ((a.d | a.dv | a.ldk | a.ldv) & 7) == 0 && ((reinterpret_cast<uintptr_t>(a.kc) | reinterpret_cast<uintptr_t>(a.vc)) & 15) == 0;
 		if (rows16 && staged <= 200 * 1024) { // rows of whole 16-byte pieces, and room for a key block
