@@ -146,10 +146,11 @@ struct MoeCombineArgs {
 	float* x_out;        // (rows, width); may be x_in
 	const SeqStep* step;
 };
+// grid (tokens, column parts): a one-token step spreads its row over several CTAs
 static __global__ void moe_combine_kernel(MoeCombineArgs a) {
 	const int t = blockIdx.x;
 	if (t >= a.step->n) return;
-	for (int c = threadIdx.x; c < a.width; c += blockDim.x) {
+	for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < a.width; c += gridDim.y * blockDim.x) {
 		float v = 0.f;
 		for (int p = 0; p < a.top; p++) {
 			const size_t pk = (size_t) t * a.top + p;
@@ -160,7 +161,8 @@ static __global__ void moe_combine_kernel(MoeCombineArgs a) {
 	}
 }
 static inline int launch_moe_combine(const MoeCombineArgs& a, int rows, cudaStream_t s) {
-	moe_combine_kernel<<<rows, norm_threads(a.width), 0, s>>>(a);
+	const int nt = norm_threads(a.width), parts = rows >= 64 ? 1 : std::min(16, (a.width + nt - 1) / nt);
+	moe_combine_kernel<<<dim3(rows, parts), nt, 0, s>>>(a);
 	return launch_check("moe_combine");
 }
 
