@@ -40,7 +40,6 @@ struct DeltaArgs {
 	const SeqStep* step;
 };
 
-__device__ __forceinline__ float softplusf_(float x) { return x > 20.f ? x : log1pf(expf(x)); }
 
 // grid (tokens, 2 G + H): a CTA convolves one head — a q head, a k head (both scaled to unit length afterwards) or a v head; the CTA of
 // the first head also computes the token's write strengths and decays

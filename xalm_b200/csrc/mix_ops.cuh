@@ -78,6 +78,7 @@ __device__ __forceinline__ float block_sum(float v, float* red) {
 struct SeqStep {
 	int pos0; // position of the step's first token in its sequence
 	int n;    // tokens in the step
+	int prev; // the token before the step's first one, -1 at a sequence's start (designs whose embedding looks at token pairs)
 };
 
 // ---- embedding -> streams -------------------------------------------------------------------------------------------------
@@ -90,6 +91,58 @@ __global__ void embed_streams_kernel(const WT* __restrict__ table, const int* __
 		const float v = ldf(row + c) * scale; // scale 1: the row as it is
 		for (int s = 0; s < S; s++) xs[(size_t) s * stream_stride + (size_t) t * width + c] = v;
 	}
+}
+
+// ---- embedding row + hashed token-pair row + grouped norm ------------------------------------------------------------------------------
+// x[t] = gnorm(table[token] * scale + pair[(prev * mul_prev + token * mul_cur) mod buckets]) * w: the pair table's last row (number `buckets`)
+// serves a sequence's first token, whose `prev` is the step's (SeqStep.prev < 0).  pair NULL: no pair rows; w NULL: no norm.  The norm is
+// the grouped RMS norm of group_norm_residual_kernel.  One CTA per token; shared memory: width + groups floats.
+struct EmbedPairArgs {
+	const void* table; // (vocab, width) bf16 or fp32
+	const void* pair;  // (buckets + 1, width) or NULL
+	float scale;
+	long long mul_prev, mul_cur;
+	int buckets;
+	const float* w;    // (width) or NULL
+	int groups, width;
+	float eps;
+	const int* tokens;
+	const SeqStep* step;
+	float* x;          // (T, width)
+};
+template <typename WT>
+__global__ void embed_pair_kernel(EmbedPairArgs a) {
+	extern __shared__ float sm[];
+	float* u = sm;
+	float* rinv = sm + a.width;
+	const int t = blockIdx.x, tid = threadIdx.x, nth = blockDim.x, lane = tid & 31, warp = tid >> 5, nw = nth >> 5;
+	if (t >= a.step->n) return;
+	const int W = a.width, tok = a.tokens[t], prev = t ? a.tokens[t - 1] : a.step->prev;
+	const WT* row = reinterpret_cast<const WT*>(a.table) + (size_t) tok * W;
+	const WT* prow = nullptr;
+	if (a.pair) {
+		const long long r = prev < 0 ? a.buckets : ((long long) prev * a.mul_prev + (long long) tok * a.mul_cur) % a.buckets;
+		prow = reinterpret_cast<const WT*>(a.pair) + (size_t) r * W;
+	}
+	for (int c = tid; c < W; c += nth) {
+		float v = ldf(row + c) * a.scale;
+		if (prow) v += ldf(prow + c);
+		u[c] = v;
+	}
+	__syncthreads();
+	if (!a.w) {
+		for (int c = tid; c < W; c += nth) a.x[(size_t) t * W + c] = u[c];
+		return;
+	}
+	const int gs = W / a.groups;
+	for (int g = warp; g < a.groups; g += nw) {
+		float ss = 0.f;
+		for (int c = lane; c < gs; c += 32) ss = fmaf(u[g * gs + c], u[g * gs + c], ss);
+		ss = warp_sum(ss);
+		if (lane == 0) rinv[g] = 1.f / sqrtf(ss / (float) gs + a.eps);
+	}
+	__syncthreads();
+	for (int c = tid; c < W; c += nth) a.x[(size_t) t * W + c] = u[c] * rinv[c / gs] * a.w[c];
 }
 
 // ---- hyper-connection read + RMS norm -------------------------------------------------------------------------------------
@@ -154,7 +207,7 @@ __global__ void hc_norm_kernel(const float* __restrict__ xs, int S, size_t strea
 // ---- fused epilogues of the row products -------------------------------------------------------------------------------------
 enum { EPI_STORE = 0, EPI_SPLIT_KV = 1, EPI_GLU = 2, EPI_HC = 3, EPI_ACT = 4 };
 enum { GLU_CLAMPED = 0, GLU_SILU = 1, GLU_GELU_TANH = 2 };
-enum { ACT_NONE = 0, ACT_RELU_SQUARED = 1, ACT_SIGMOID = 2, ACT_SILU = 3 };
+enum { ACT_NONE = 0, ACT_RELU_SQUARED = 1, ACT_SIGMOID = 2, ACT_SILU = 3, ACT_GELU_TANH = 4, ACT_SIGMOID_POW = 5 };
 struct RowsEpi {
 	int kind = EPI_STORE;
 	float* out = nullptr; // STORE / SPLIT_KV / ACT: (T, ldo); GLU: (T, ldo) with ldo = N / 2
@@ -164,8 +217,11 @@ struct RowsEpi {
 	float cap = 0.f;
 	const float* mul = nullptr;
 	int ldm = 0, mul_act = ACT_SIGMOID;
-	// ACT: v <- act(v), no gate
+	// ACT: v <- act(v + bias[col]), no gate.  ACT_SIGMOID_POW: sigmoid(.)^act_pow, as exp(act_pow * log sigmoid(.)) (a decay in (0, 1) whose
+	// logarithm stays exact where the sigmoid itself would leave the fp32 range)
 	int act = ACT_NONE;
+	const float* bias = nullptr;
+	float act_pow = 1.f;
 	// batched products (blockIdx.z = b): A advances by batch_a floats, W by batch_w elements, the output (and mul) by batch_o columns.
 	// One launch then runs a product per head on that head's slice of the rows.
 	int batch_a = 0, batch_o = 0;
@@ -199,13 +255,16 @@ __device__ __forceinline__ float glu_clamped(float g, float u, float limit, floa
 	return g * sigmoidf_(alpha * g) * (u + 1.f);
 }
 
-__device__ __forceinline__ float act_apply(int act, float v) {
+__device__ __forceinline__ float gelu_tanhf_(float z) { return 0.5f * z * (1.f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z))); }
+__device__ __forceinline__ float log_sigmoidf_(float z) { return fminf(z, 0.f) - log1pf(expf(-fabsf(z))); }
+__device__ __forceinline__ float act_apply(int act, float v, float p = 1.f) {
 	if (act == ACT_RELU_SQUARED) { v = fmaxf(v, 0.f); return v * v; }
 	if (act == ACT_SIGMOID) return sigmoidf_(v);
 	if (act == ACT_SILU) return v * sigmoidf_(v);
+	if (act == ACT_GELU_TANH) return gelu_tanhf_(v);
+	if (act == ACT_SIGMOID_POW) return expf(p * log_sigmoidf_(v));
 	return v;
 }
-__device__ __forceinline__ float gelu_tanhf_(float z) { return 0.5f * z * (1.f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z))); }
 __device__ __forceinline__ float glu_apply(int act, float g, float u, float limit, float alpha) {
 	if (act == GLU_SILU) return g * sigmoidf_(g) * u;
 	if (act == GLU_GELU_TANH) return gelu_tanhf_(g) * u;
@@ -235,7 +294,7 @@ __device__ __forceinline__ void epi_apply(const RowsEpi& e, int row, int col, in
 			if (e.mul) v *= act_apply(e.mul_act, e.mul[(size_t) row * e.ldm + col]);
 			e.out[(size_t) row * e.ldo + col] = v;
 			break;
-		case EPI_ACT: e.out[(size_t) row * e.ldo + col] = act_apply(e.act, v); break;
+		case EPI_ACT: e.out[(size_t) row * e.ldo + col] = act_apply(e.act, e.bias ? v + e.bias[col] : v, e.act_pow); break;
 		case EPI_SPLIT_KV: {
 			if (col < e.n_plain) {
 				if (col >= e.silu_off && col < e.silu_off + e.silu_n) v = v * sigmoidf_(v);
@@ -434,6 +493,8 @@ struct SwaArgs {
 	const float* r1;   // distance bias r1[h] * log1p(r2[h] * (i - j)) taken off the score; NULL: none
 	const float* r2;
 	const float* talk; // (H, H) score_h <- sum_g talk[h, g] score_g; NULL: none
+	const float* sink; // (H) the softmax's denominator also holds exp(sink[h]): a key of no position and no value that is not scaled; NULL: none
+	float out_scale;   // multiplies the result (0: 1)
 	const SeqStep* step;
 	float* out;        // (T, ldo): head h at columns h * dv
 	int ldo;           // 0: H * dv.  The launcher runs the heads of a single-group attention in several launches when all of them do not fit one
@@ -470,6 +531,20 @@ __device__ __forceinline__ SwaKeys swa_keys(int window, int keep_first, int ring
 	return k;
 }
 
+// o = num / (den + exp(sink - m)), num and den being sums of exp(score - m); written so that a sink far above every score cannot overflow
+__device__ __forceinline__ float swa_finish(const SwaArgs& a, int h, float num, float den, float m) {
+	if (a.sink) {
+		const float sk = a.sink[h];
+		if (sk > m) {
+			const float c = expf(m - sk);
+			num *= c;
+			den = fmaf(den, c, 1.f);
+		} else den += expf(sk - m);
+	}
+	const float o = num / den;
+	return a.out_scale != 0.f ? o * a.out_scale : o;
+}
+
 // joins the key splits of rows [t_first, t_first + rows): out = (sum_s e^{m_s - m} O_s) / (sum_s e^{m_s - m} l_s), then the gate
 __device__ __forceinline__ void swa_merge_one(const SwaArgs& a, int t, int hc) {
 	const int H = a.H, dv = a.dv, ns = a.n_splits, h = hc / dv;
@@ -501,7 +576,7 @@ __device__ __forceinline__ void swa_merge_one(const SwaArgs& a, int t, int hc) {
 				den = fmaf(w, ls[u], den);
 			}
 	}
-	float o = num / den;
+	float o = swa_finish(a, h, num, den, m);
 	if (a.gate) o *= sigmoidf_(a.gate[(size_t) t * a.ldg + a.g_off + hc]);
 	a.out[(size_t) t * (a.ldo ? a.ldo : H * dv) + hc] = o;
 }
@@ -717,7 +792,7 @@ __global__ void __launch_bounds__(256) swa_attn_kernel(SwaArgs a) {
 	}
 	if (a.n_splits == 1) {
 		for (int x = tid; x < H * dv; x += nth) {
-			float o = O[x] / lrun[x / dv];
+			float o = swa_finish(a, x / dv, O[x], lrun[x / dv], mrun[x / dv]);
 			if (a.gate) o *= sigmoidf_(a.gate[(size_t) t * a.ldg + a.g_off + x]);
 			a.out[(size_t) t * (a.ldo ? a.ldo : H * dv) + x] = o;
 		}
@@ -1007,7 +1082,7 @@ __global__ void __launch_bounds__(256) swa_tile_kernel(SwaArgs a) {
 		const int t = t0 + q;
 		const float acc = O[(size_t) row * dvp + c];
 		if (a.n_splits == 1) {
-			float o = acc / lrun[row];
+			float o = swa_finish(a, h, acc, lrun[row], mrun[row]);
 			if (a.gate) o *= sigmoidf_(a.gate[(size_t) t * a.ldg + a.g_off + h * dv + c]);
 			a.out[(size_t) t * (a.ldo ? a.ldo : H * dv) + h * dv + c] = o;
 		} else a.part_o[((size_t) t * a.n_splits + sp) * (H * dv) + h * dv + c] = acc;
@@ -1044,8 +1119,31 @@ struct Hgrn2Args {
 	int norm_plain;      // 1: o over its root mean square with no weight (norm_w NULL)
 	const float* gate;   // (T, ldg): o <- o * silu(gate[t, g_off + h * dv + c]) after the norm; NULL: none
 	int ldg, g_off;
+	// Keyed modes: S_t = diag(f_t) S_{t-1} + (s_t k_t) v_t^T, o_t = S_t^T (q_scale q_t) + skip[h] v_t, with q and k taken as they are from
+	// q_off / k_off + (h / qk_rep) * d (qk_rep neighbouring heads share them; 0: 1).
+	//   keyed 1: one decay per key channel, ready-made at f_off + h * d + i; s = 1                                  (gated linear attention)
+	//   keyed 2: one step size per head and token, dt = softplus(proj[dt_off + h] + dt_bias[h]); f = exp(-exp(A_log[h]) dt) on every
+	//            channel, s = dt                                                                                  (state-space duality)
+	int keyed;
+	int qk_rep;
+	float q_scale;       // 0: 1
+	int dt_off;
+	const float *dt_bias, *A_log; // (H)
+	const float* skip;   // (H) or NULL
 };
 constexpr int HG_TC = 8; // tokens staged at a time
+__device__ __forceinline__ float softplusf_(float x) { return x > 20.f ? x : log1pf(expf(x)); }
+// decay, key factor and query of channel i of head h for one token's row, in a keyed mode
+__device__ __forceinline__ void hgrn2_keyed(const Hgrn2Args& a, int h, float f_raw, float k_raw, float q_raw, float& f, float& g, float& q) {
+	float s = 1.f;
+	f = f_raw;
+	if (a.keyed == 2) {
+		s = softplusf_(f_raw + a.dt_bias[h]);
+		f = expf(-expf(a.A_log[h]) * s);
+	}
+	g = k_raw * s;
+	q = a.q_scale != 0.f ? q_raw * a.q_scale : q_raw;
+}
 
 static __global__ void hgrn2_kernel(Hgrn2Args a) {
 	extern __shared__ float sm[];
@@ -1064,6 +1162,11 @@ static __global__ void hgrn2_kernel(Hgrn2Args a) {
 		for (int x = tid; x < nt * d; x += nth) {
 			const int tt = x / d, i = x % d;
 			const float* row = a.proj + (size_t) (t0 + tt) * a.ld;
+			if (a.keyed) {
+				const int hk = h / max(a.qk_rep, 1);
+				hgrn2_keyed(a, h, a.keyed == 2 ? row[a.dt_off + h] : row[a.f_off + h * d + i], row[a.k_off + hk * d + i], row[a.q_off + hk * d + i], fch[x], gch[x], qch[x]);
+				continue;
+			}
 			const float zq = row[a.q_off + h * d + i];
 			if (a.decay) {
 				fch[x] = a.decay[h];
@@ -1091,7 +1194,7 @@ static __global__ void hgrn2_kernel(Hgrn2Args a) {
 					S[(size_t) i * dv + c] = s;
 					o = fmaf(s, q[i], o);
 				}
-				och[tt * dv + c] = o;
+				och[tt * dv + c] = a.skip ? fmaf(a.skip[h], v, o) : o;
 			}
 		}
 		__syncthreads();
@@ -1142,7 +1245,7 @@ __device__ __forceinline__ float warp_sum_transposed32(float (&v)[32], int lane)
 	return v[0];
 }
 
-template <int DPL>
+template <int DPL, int KEYED>
 __global__ void hgrn2_cols_kernel(Hgrn2Args a) {
 	namespace cg = cooperative_groups;
 	cg::cluster_group cluster = cg::this_cluster();
@@ -1166,17 +1269,25 @@ __global__ void hgrn2_cols_kernel(Hgrn2Args a) {
 		}
 	// The next tile's inputs travel through registers while this tile is scanned: raw loads are issued before the scan, the
 	// activations (unless the producer already applied them) and the stores to the other buffer come after it.
-	float rf[NPF], rq[NPF], rv = 0.f;
+	float rf[NPF], rq[NPF], rk[KEYED ? NPF : 1], rv = 0.f;
+	const int hk = KEYED ? h / max(a.qk_rep, 1) : h;
 	auto fetch = [&](int t0) {
 		const int nt = min(HG_TT, T - t0);
 #pragma unroll
 		for (int u = 0; u < NPF; u++) {
 			const int x = tid + u * nth, tt = x / DP, i = x % DP;
 			rf[u] = 0.f; rq[u] = 0.f;
+			if (KEYED) rk[KEYED ? u : 0] = 0.f;
 			if (x < HG_TT * DP && tt < nt && i < d) {
 				const float* row = a.proj + (size_t) (t0 + tt) * a.ld;
-				rf[u] = row[(a.decay ? a.k_off : a.f_off) + h * d + i];
-				rq[u] = row[a.q_off + h * d + i];
+				if (KEYED) {
+					rf[u] = a.keyed == 2 ? row[a.dt_off + h] : row[a.f_off + h * d + i];
+					rk[KEYED ? u : 0] = row[a.k_off + hk * d + i];
+					rq[u] = row[a.q_off + hk * d + i];
+				} else {
+					rf[u] = row[(a.decay ? a.k_off : a.f_off) + h * d + i];
+					rq[u] = row[a.q_off + h * d + i];
+				}
 			}
 		}
 		const int tt = tid / cpb, c = c_blk + tid % cpb; // nth == HG_TT * cpb
@@ -1190,7 +1301,8 @@ __global__ void hgrn2_cols_kernel(Hgrn2Args a) {
 			if (x < HG_TT * DP) {
 				float f = 0.f, g = 0.f, q = 0.f;
 				if (tt < nt && i < d) {
-					if (a.decay) { f = a.decay[h]; g = rf[u] * a.k_scale; q = rq[u]; }
+					if (KEYED) hgrn2_keyed(a, h, rf[u], rk[KEYED ? u : 0], rq[u], f, g, q);
+					else if (a.decay) { f = a.decay[h]; g = rf[u] * a.k_scale; q = rq[u]; }
 					else {
 						if (a.activated) { f = rf[u]; q = rq[u]; }
 						else {
@@ -1240,7 +1352,8 @@ __global__ void hgrn2_cols_kernel(Hgrn2Args a) {
 				}
 			}
 		}
-		const float o = warp_sum_transposed32(p, lane); // lane = tt * HG_CW + cc
+		float o = warp_sum_transposed32(p, lane); // lane = tt * HG_CW + cc
+		if (KEYED && a.skip) o = fmaf(a.skip[h], vch[(lane / HG_CW) * cpb + warp * HG_CW + lane % HG_CW], o);
 		och[(lane / HG_CW) * cpb + warp * HG_CW + lane % HG_CW] = o;
 		if (more) stage(sm + (cur ^ 1) * tile_floats, t0 + HG_TT);
 		__syncthreads();
@@ -1487,6 +1600,10 @@ struct GroupNormArgs {
 	const float* dwa = nullptr;    // (n_hist + 1)
 	float* avg_out = nullptr;      // (rows, width)
 	float* keep_out = nullptr;     // (rows, width) or NULL
+	const float* gate = nullptr;   // (rows, ldg) or NULL: y <- y * silu(gate) before the norm (a gated recurrence whose norm follows the gate)
+	int ldg = 0;
+	float out_scale = 0.f;         // multiplies the normed, weighted row (0: 1)
+	int ld_out = 0;                // elements between rows of x_out (0: width): the result may be a run of columns of a wider buffer
 };
 static __global__ void group_norm_residual_kernel(GroupNormArgs a) {
 	extern __shared__ float sm[];
@@ -1509,6 +1626,10 @@ static __global__ void group_norm_residual_kernel(GroupNormArgs a) {
 						v[k] = fmaf(a.part_w[pk], a.y[(a.part_row ? (size_t) a.part_row[pk] : pk) * a.ldy + c], v[k]);
 					}
 				} else v[k] = a.y[(size_t) t * a.ldy + c];
+				if (a.gate) {
+					const float z = a.gate[(size_t) t * a.ldg + c];
+					v[k] *= z * sigmoidf_(z);
+				}
 			}
 		}
 #pragma unroll
@@ -1548,8 +1669,9 @@ static __global__ void group_norm_residual_kernel(GroupNormArgs a) {
 			if (c >= W) continue;
 			const size_t at = (size_t) t * W + c;
 			float v = u[c] * rinv[c / gs] * wv[k];
+			if (a.out_scale != 0.f) v *= a.out_scale;
 			if (a.x_in) v += xi[k];
-			a.x_out[at] = v;
+			a.x_out[a.ld_out ? (size_t) t * a.ld_out + c : at] = v;
 			if (a.dwa) {
 				v = fmaf(a.dwa[a.n_hist], v, acc[k]);
 				a.avg_out[at] = v;
@@ -1585,6 +1707,7 @@ struct QkvPostArgs {
 	const float *bq, *bk, *bv; // biases of the three projections, or NULL
 	const float* freq;         // (rot_half) or NULL
 	int rot_half;
+	float rot_mag;             // multiplies cos and sin of every turn (a rescaled rotation changes the length of what it turns); 0: 1
 	int norm_qk, norm_v;
 	float eps;
 	void *kc, *vc;
@@ -1611,6 +1734,7 @@ static __global__ void qkv_post_kernel(QkvPostArgs a) {
 		for (int c = lane; c < r; c += 32) {
 			float sn, cs;
 			sincosf((float) pos * a.freq[c], &sn, &cs);
+			if (a.rot_mag != 0.f) { sn *= a.rot_mag; cs *= a.rot_mag; }
 			const float p = x[c], q = x[c + r];
 			x[c] = p * cs - q * sn;
 			x[c + r] = q * cs + p * sn;
@@ -1641,6 +1765,16 @@ static inline int launch_qkv_post(const QkvPostArgs& a, int rows, cudaStream_t s
 	if ((size_t) nw * wmax * 4 > 48 * 1024) return set_error(XALM_ERR_UNSUPPORTED, "qkv_post: heads of %d do not fit shared memory", wmax);
 	qkv_post_kernel<<<dim3(rows, (units + nw - 1) / nw), nw * 32, (size_t) nw * wmax * 4, s>>>(a);
 	return launch_check("qkv_post");
+}
+
+static inline int launch_embed_pair(const EmbedPairArgs& a, bool w_bf16, int rows, cudaStream_t s) {
+	if (a.w && (a.groups <= 0 || a.width % a.groups)) return set_error(XALM_ERR_INVALID, "embedding norm: %d groups do not divide a row of %d", a.groups, a.width);
+	if (a.pair && a.buckets <= 0) return set_error(XALM_ERR_INVALID, "pair embedding: %d buckets", a.buckets);
+	const size_t smem = (size_t) (a.width + std::max(a.groups, 1)) * 4;
+	if (smem > 48 * 1024) return set_error(XALM_ERR_UNSUPPORTED, "embedding: a row of %d does not fit shared memory", a.width);
+	if (w_bf16) embed_pair_kernel<__nv_bfloat16><<<rows, norm_threads(a.width), smem, s>>>(a);
+	else embed_pair_kernel<float><<<rows, norm_threads(a.width), smem, s>>>(a);
+	return launch_check("embed_pair");
 }
 
 static inline int launch_rows_epilogue(const float* src, int lds, int T, int N, const RowsEpi& e, cudaStream_t s) {
@@ -1705,6 +1839,7 @@ static inline int launch_swa(SwaArgs a, int rows, bool cache_f32, cudaStream_t s
 				b.ldo = a.H * a.dv;
 				b.q_off = a.q_off + z * Hc * a.d;
 				b.g_off = a.g_off + z * Hc * a.dv;
+				if (a.sink) b.sink = a.sink + (size_t) z * Hc;
 				b.out = a.out + (size_t) z * Hc * a.dv;
 				if (a.part_o) b.part_o = a.part_o + (size_t) z * cap * Hc * a.dv;
 				if (a.part_ml) b.part_ml = a.part_ml + (size_t) z * cap * Hc * 2;
@@ -1760,10 +1895,10 @@ static inline int launch_swa(SwaArgs a, int rows, bool cache_f32, cudaStream_t s
 
 // max_rows: an upper bound of the step's tokens known on the host.  The cluster kernel takes d <= 256 and dv <= 1024; anything else
 // (and max_rows beyond its shared memory) runs the one-CTA-per-head kernel.
-template <int DPL>
+template <int DPL, int KEYED>
 static inline int launch_hgrn2_cols(const Hgrn2Args& a, int warps, int nb, cudaStream_t s) {
 	const size_t smem = hgrn2_cols_smem_bytes(DPL, warps, a.max_rows);
-	if (smem > 48 * 1024) XALM_CUDA_CHECK(cudaFuncSetAttribute(hgrn2_cols_kernel<DPL>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem));
+	if (smem > 48 * 1024) XALM_CUDA_CHECK(cudaFuncSetAttribute(hgrn2_cols_kernel<DPL, KEYED>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem));
 	cudaLaunchConfig_t cfg = {};
 	cfg.gridDim = dim3(nb, a.H);
 	cfg.blockDim = dim3(warps * 32);
@@ -1774,7 +1909,7 @@ static inline int launch_hgrn2_cols(const Hgrn2Args& a, int warps, int nb, cudaS
 	at[0].val.clusterDim.x = nb; at[0].val.clusterDim.y = 1; at[0].val.clusterDim.z = 1;
 	cfg.attrs = at;
 	cfg.numAttrs = 1;
-	const cudaError_t e = cudaLaunchKernelEx(&cfg, hgrn2_cols_kernel<DPL>, a);
+	const cudaError_t e = cudaLaunchKernelEx(&cfg, hgrn2_cols_kernel<DPL, KEYED>, a);
 	if (e != cudaSuccess) return set_error(XALM_ERR_CUDA, "hgrn2 launch failed: %s", cudaGetErrorString(e));
 	return XALM_OK;
 }
@@ -1785,9 +1920,27 @@ static inline int hgrn2_cols_warps(int dv) {
 	while (warps < 32 && (dv + warps * HG_CW - 1) / (warps * HG_CW) > 8) warps *= 2;
 	return warps;
 }
-static inline bool hgrn2_cols_ok(int d, int dv, int max_rows) {
+// registers per thread of the instance that serves dpl channels per lane, as compiled (asked of the runtime once; a table if it will not say)
+static inline int hgrn2_cols_regs(int dpl, bool keyed) {
+	static int known[2][4] = {};
+	const int slot = dpl <= 1 ? 0 : dpl <= 2 ? 1 : dpl <= 4 ? 2 : 3;
+	int& r = known[keyed ? 1 : 0][slot];
+	if (!r) {
+		cudaFuncAttributes at = {};
+		cudaError_t e;
+		if (keyed) e = slot == 0 ? cudaFuncGetAttributes(&at, hgrn2_cols_kernel<1, 1>) : slot == 1 ? cudaFuncGetAttributes(&at, hgrn2_cols_kernel<2, 1>)
+		             : slot == 2 ? cudaFuncGetAttributes(&at, hgrn2_cols_kernel<4, 1>) : cudaFuncGetAttributes(&at, hgrn2_cols_kernel<8, 1>);
+		else e = slot == 0 ? cudaFuncGetAttributes(&at, hgrn2_cols_kernel<1, 0>) : slot == 1 ? cudaFuncGetAttributes(&at, hgrn2_cols_kernel<2, 0>)
+		         : slot == 2 ? cudaFuncGetAttributes(&at, hgrn2_cols_kernel<4, 0>) : cudaFuncGetAttributes(&at, hgrn2_cols_kernel<8, 0>);
+		if (e != cudaSuccess) cudaGetLastError();
+		r = e == cudaSuccess && at.numRegs > 0 ? (at.numRegs + 7) / 8 * 8 : slot == 0 ? 64 : slot == 1 ? 112 : slot == 2 ? 128 : 240;
+	}
+	return r;
+}
+static inline bool hgrn2_cols_ok(int d, int dv, int max_rows, bool keyed = false) {
 	const int warps = hgrn2_cols_warps(dv), nb = (dv + warps * HG_CW - 1) / (warps * HG_CW), dpl = (d + 31) / 32;
-	const int regs = dpl <= 1 ? 64 : dpl <= 4 ? 96 : 216; // per thread, as compiled; a CTA's registers must fit one SM's file
+	if (dpl > 8) return false;
+	const int regs = hgrn2_cols_regs(dpl, keyed); // a CTA's registers must fit one SM's file
 	return nb <= 8 && dpl <= 8 && warps * 32 * regs <= 65536 && max_rows > 0 && hgrn2_cols_smem_bytes(dpl <= 1 ? 1 : dpl <= 2 ? 2 : dpl <= 4 ? 4 : 8, warps, max_rows) <= 160 * 1024;
 }
 
@@ -1795,11 +1948,18 @@ static inline int launch_hgrn2(const Hgrn2Args& a, cudaStream_t s) {
 	const int warps = hgrn2_cols_warps(a.dv);
 	const int nb = (a.dv + warps * HG_CW - 1) / (warps * HG_CW);
 	const int dpl = (a.d + 31) / 32;
-	if (hgrn2_cols_ok(a.d, a.dv, a.max_rows)) {
-		if (dpl <= 1) return launch_hgrn2_cols<1>(a, warps, nb, s);
-		if (dpl <= 2) return launch_hgrn2_cols<2>(a, warps, nb, s);
-		if (dpl <= 4) return launch_hgrn2_cols<4>(a, warps, nb, s);
-		return launch_hgrn2_cols<8>(a, warps, nb, s);
+	if (a.keyed && a.H % std::max(a.qk_rep, 1)) return set_error(XALM_ERR_INVALID, "recurrence: %d heads in groups of %d", a.H, a.qk_rep);
+	if (hgrn2_cols_ok(a.d, a.dv, a.max_rows, a.keyed != 0)) {
+		if (a.keyed) {
+			if (dpl <= 1) return launch_hgrn2_cols<1, 1>(a, warps, nb, s);
+			if (dpl <= 2) return launch_hgrn2_cols<2, 1>(a, warps, nb, s);
+			if (dpl <= 4) return launch_hgrn2_cols<4, 1>(a, warps, nb, s);
+			return launch_hgrn2_cols<8, 1>(a, warps, nb, s);
+		}
+		if (dpl <= 1) return launch_hgrn2_cols<1, 0>(a, warps, nb, s);
+		if (dpl <= 2) return launch_hgrn2_cols<2, 0>(a, warps, nb, s);
+		if (dpl <= 4) return launch_hgrn2_cols<4, 0>(a, warps, nb, s);
+		return launch_hgrn2_cols<8, 0>(a, warps, nb, s);
 	}
 	const size_t smem = hgrn2_smem_bytes(a.d, a.dv);
 	XALM_TRY(hgrn2_prepare(a.d, a.dv));

@@ -1,4 +1,4 @@
-// seq_family.cuh — the sequence engine shared by the model families that a config.json describes (Nabalix, Bolovik, Duletar): what a
+// seq_family.cuh — the sequence engine shared by the model families that a config.json describes (Nabalix, Bolovik, Duletar, Kubolorn): what a
 // family does NOT write itself.
 //
 //   * tensors by name: the family lists what it reads (expect), the loader uploads them (any order, fp32 / fp16 / bf16), finalize
@@ -95,6 +95,7 @@ struct SeqModel { // what a handle of these families points to (ModelHead first)
 	cudaEvent_t ev_fork = nullptr, ev_join = nullptr;
 	cudaGraphExec_t graph[2] = {nullptr, nullptr};
 	int pos = 0; // tokens the running sequence holds
+	int prev_token = -1; // the last of them (-1: none yet), handed to the kernels as SeqStep.prev
 	int last_launches = 0;
 	bool use_tc = false;
 	long long weight_bytes = 0, weight_bytes_tc = 0;
@@ -270,7 +271,7 @@ int ensure_graph(SeqModel* m, int mode) {
 int run_pass(SeqModel* m, const int* tokens, int n, int want) {
 	for (int i = 0; i < n; i++)
 		if (tokens[i] < 0 || tokens[i] >= m->vocab) return set_error(XALM_ERR_INVALID, "token %d out of range", tokens[i]);
-	const SeqStep st = {m->pos, n};
+	const SeqStep st = {m->pos, n, m->prev_token};
 	XALM_CUDA_CHECK(cudaMemcpyAsync(m->d_tokens, tokens, (size_t) n * 4, cudaMemcpyHostToDevice, m->stream));
 	XALM_CUDA_CHECK(cudaMemcpyAsync(m->d_step, &st, sizeof st, cudaMemcpyHostToDevice, m->stream));
 	int nl = 0;
@@ -284,6 +285,7 @@ int run_pass(SeqModel* m, const int* tokens, int n, int want) {
 	}
 	m->last_launches = nl;
 	m->pos += n;
+	m->prev_token = tokens[n - 1];
 	return XALM_OK;
 }
 
@@ -376,9 +378,10 @@ int seq_upload(SeqModel* m, const char* name, int type_id, const int* shape, int
 	HostTensor& t = it->second;
 	bool same = (size_t) rank == t.shape.size();
 	size_t count = 1;
-	for (int i = 0; same && i < rank; i++) same = shape[i] == t.shape[(size_t) i];
-	for (int dsz : t.shape) count *= (size_t) dsz;
+	for (int i = 0; same && i < rank; i++) same = shape[i] == t.shape[(size_t) i] || (t.shape[(size_t) i] < 0 && shape[i] > 0); // a negative extent: whatever the file has
 	if (!same) return set_error(XALM_ERR_INVALID, "shape mismatch for %s", name);
+	for (int i = 0; i < rank; i++) t.shape[(size_t) i] = shape[i];
+	for (int dsz : t.shape) count *= (size_t) dsz;
 	const size_t esz = type_id == XALM_F32 ? 4 : (type_id == XALM_F16 || type_id == XALM_BF16) ? 2 : 0;
 	if (!esz) return set_error(XALM_ERR_UNSUPPORTED, "tensor %s: type %d (F32, F16 or BF16)", name, type_id);
 	if (nbytes != count * esz) return set_error(XALM_ERR_INVALID, "size mismatch for %s", name);
@@ -399,7 +402,7 @@ int seq_upload(SeqModel* m, const char* name, int type_id, const int* shape, int
 	return XALM_OK;
 }
 
-// embedding table, head matrix and final norm weight are named alike in these families
+// embedding table, head matrix (absent: the embedding table serves) and final norm weight are named alike in these families
 int seq_finalize(SeqModel* m) {
 	if (!m) return set_error(XALM_ERR_INVALID, "model is NULL");
 	if (m->finalized) return XALM_OK;
@@ -414,8 +417,9 @@ int seq_finalize(SeqModel* m) {
 	m->keep_layers = getenv("XALM_SEQ_KEEP_LAYERS") ? atoi(getenv("XALM_SEQ_KEEP_LAYERS")) : 0;
 	m->use_tc = m->w_bf16 && tune("seq_tc") > 0;
 	m->tc_min_rows = std::max(1, tune("seq_tc_min"));
-	XALM_TRY(upload_rows(m, {tensor_or_null(m, "embed")}, W, false, &m->embed, nullptr));
-	XALM_TRY(upload_rows(m, {tensor_or_null(m, "head")}, W, false, &m->w_head, &m->m_head));
+	XALM_TRY(upload_rows(m, {tensor_or_null(m, "embed")}, W, false, &m->embed, &m->m_head));
+	if (m->tensors.count("head")) XALM_TRY(upload_rows(m, {tensor_or_null(m, "head")}, W, false, &m->w_head, &m->m_head));
+	else m->w_head = m->embed; // a family that lists no head matrix multiplies by the embedding table itself
 	XALM_TRY(upload_vec(m, "final.norm", &m->final_norm));
 	XALM_TRY(m->hooks->finalize(m));
 	if (m->use_tc) {
@@ -444,6 +448,7 @@ int seq_release(SeqModel* m) {
 	XALM_TRY(m->hooks->release(m));
 	XALM_CUDA_CHECK(cudaStreamSynchronize(m->stream));
 	m->pos = 0;
+	m->prev_token = -1;
 	return XALM_OK;
 }
 
