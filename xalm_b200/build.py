@@ -44,8 +44,9 @@ def _sources(d, exts):
 # build_cuda(families=["Nabalix"]) compiles abi.cu and what FAMILY_TUS names for those families, nothing else; the list of
 # linked units is kept beside the objects, and a later call that asks for more relinks.
 FAMILY_TUS = {"Llama": ["xalm_cuda.cu", "prefill.cu", "decode_mega.cu"], "Nabalix": ["nabalix.cu", "mix_ops.cu", "prefill.cu"],
-              "Bolovik": ["bolovik.cu", "mix_ops.cu", "prefill.cu"], "Duletar": ["duletar.cu", "mix_ops.cu", "prefill.cu"]}
-CUDA_TUS = ["abi.cu", "xalm_cuda.cu", "prefill.cu", "decode_mega.cu", "nabalix.cu", "bolovik.cu", "duletar.cu", "mix_ops.cu"]
+              "Bolovik": ["bolovik.cu", "mix_ops.cu", "prefill.cu"], "Duletar": ["duletar.cu", "mix_ops.cu", "prefill.cu"],
+              "Kubolorn": ["kubolorn.cu", "mix_ops.cu", "prefill.cu"]}
+CUDA_TUS = ["abi.cu", "xalm_cuda.cu", "prefill.cu", "decode_mega.cu", "nabalix.cu", "bolovik.cu", "duletar.cu", "kubolorn.cu", "mix_ops.cu"]
 
 
 def _tus(families):
