@@ -205,6 +205,36 @@ int xalm_cuda_latent_attend(float* out, const float* q, const float* cache, cons
                             const float* uk, const float* uv, const float* freq, float scale, int n_splits, int cache_bf16, int w_bf16);
 int xalm_cuda_rows_act(float* out, const float* x, const float* w, int T, int N, int K, int act, float cap, const float* mul, int mul_act, int w_bf16);
 
+/* Mechanisms of designs with convolved readers, keyed recurrences and sink attention, as ops (host arrays in and out, the same kernels):
+ * norm_conv: for each of `readers` (1 or 2) readers r of the same rows x (T, W): h = grouped RMS norm of x (groups equal parts, each over
+ *   its own sqrt(mean + eps)) times w[r], out[r] = h + causal depthwise convolution of h over time with cw[r] (W, taps), last column = the
+ *   current row.  hist (readers, taps - 1, W): the normed rows before x[0], oldest first; rewritten with the last taps - 1 normed rows.
+ * short_conv: out[t, c] = act(bias[c] + sum_j w[c, j] x[t - taps + 1 + j, c]) (act 0 none, 3 silu), hist (taps - 1, C) raw inputs as above.
+ * embed_pair: out[t] = grouped norm(table[token_t] * scale + pair[(token_{t-1} * mul_prev + token_t * mul_cur) mod buckets]) * w, the row
+ *   `buckets` of pair where there is no previous token (prev < 0 for t = 0); pair NULL: no pair rows; w NULL: no norm.
+ * keyed_recurrence: per head S_t = diag(f_t) S_{t-1} + (s_t k_t) v_t^T, o_t = S_t^T (q_scale q_t) + skip[h] v_t; q, k (T, H / rep * d) shared by
+ *   `rep` neighbouring heads.  mode 1: f (T, H d) decays as they are, s = 1.  mode 2: f (T, H) raw step sizes, dt = softplus(f + dt_bias[h]),
+ *   decay exp(-exp(A_log[h]) dt) on every channel, s = dt.  Then, when given: o over its root mean square times norm_w (dv), times silu(gate).
+ * sink_attention: causal softmax attention of H heads over G key heads whose denominator also holds exp(sink[h]); result times out_scale
+ *   (0: 1).  k (pos0 + T, G d), v (pos0 + T, G dv).
+ * qk_post: proj (T, (H + G) d) = [q | k]; q_out = turned q; k_out (ring, G d) the turned keys and v_out (ring, G d) the keys as they came, row
+ *   p % ring for position p.  Turn: the first 2 rot_half entries of a head, entry i with i + rot_half, by p * freq[i], cos and sin times rot_mag.
+ * rows_act_bias: out = act(x W^T + bias); act as rows_act, 4 tanh-gelu, 5 sigmoid(.)^act_pow.
+ * gated_group_norm: out[:, :W] of rows ld_out wide = grouped RMS norm of y * silu(gate) (gate NULL: of y), times w, times out_scale (0: 1). */
+int xalm_cuda_norm_conv(float* out, float* hist, const float* x, int T, int W, int groups, int taps, int readers, const float* w, const float* cw, float eps);
+int xalm_cuda_short_conv(float* out, float* hist, const float* x, int T, int C, int taps, const float* w, const float* bias, int act);
+int xalm_cuda_embed_pair(float* out, const int* tokens, int T, int prev, const float* table, int vocab, const float* pair, int buckets, int mul_prev,
+                         int mul_cur, float scale, const float* w, int groups, int W, float eps);
+int xalm_cuda_keyed_recurrence(float* out, float* state, const float* q, const float* k, const float* v, const float* f, int T, int H, int rep, int d, int dv,
+                               int mode, float q_scale, const float* dt_bias, const float* A_log, const float* skip, const float* norm_w, const float* gate,
+                               float eps);
+int xalm_cuda_sink_attention(float* out, const float* q, const float* k, const float* v, int T, int pos0, int H, int G, int d, int dv, float scale,
+                             const float* sink, float out_scale, int n_splits, int cache_bf16);
+int xalm_cuda_qk_post(float* q_out, float* k_out, float* v_out, const float* proj, int T, int pos0, int H, int G, int d, const float* freq, int rot_half,
+                      float rot_mag, int ring);
+int xalm_cuda_rows_act_bias(float* out, const float* x, const float* w, int T, int N, int K, int act, const float* bias, float act_pow, int w_bf16);
+int xalm_cuda_gated_group_norm(float* out, const float* y, const float* gate, const float* w, int T, int W, int groups, float eps, float out_scale, int ld_out);
+
 /* Tensor parallel plumbing (no reference analogue; north star).  Rank 0 makes an id, the host side ships it to
  * the other ranks (torch.distributed / MPI / a file), every rank calls comm_init before finalize. */
 #define XALM_COMM_ID_BYTES 128

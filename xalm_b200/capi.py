@@ -101,6 +101,14 @@ SYMBOLS = {
     "xalm_cuda_latent_post": (_i, [_vp] * 3 + [_i] * 5 + [_vp] * 3 + [C.c_float, _i, _i]),
     "xalm_cuda_latent_attend": (_i, [_vp] * 4 + [_i] * 8 + [_vp] * 3 + [C.c_float, _i, _i, _i]),
     "xalm_cuda_rows_act": (_i, [_vp] * 3 + [_i] * 4 + [C.c_float, _vp, _i, _i]),
+    "xalm_cuda_norm_conv": (_i, [_vp] * 3 + [_i] * 5 + [_vp, _vp, C.c_float]),
+    "xalm_cuda_short_conv": (_i, [_vp] * 3 + [_i] * 3 + [_vp, _vp, _i]),
+    "xalm_cuda_embed_pair": (_i, [_vp, _vp, _i, _i, _vp, _i, _vp, _i, _i, _i, C.c_float, _vp, _i, _i, C.c_float]),
+    "xalm_cuda_keyed_recurrence": (_i, [_vp] * 6 + [_i] * 6 + [C.c_float] + [_vp] * 5 + [C.c_float]),
+    "xalm_cuda_sink_attention": (_i, [_vp] * 4 + [_i] * 6 + [C.c_float, _vp, C.c_float, _i, _i]),
+    "xalm_cuda_qk_post": (_i, [_vp] * 4 + [_i] * 5 + [_vp, _i, C.c_float, _i]),
+    "xalm_cuda_rows_act_bias": (_i, [_vp] * 3 + [_i] * 4 + [_vp, C.c_float, _i]),
+    "xalm_cuda_gated_group_norm": (_i, [_vp] * 4 + [_i] * 3 + [C.c_float, C.c_float, _i]),
 }
 PRECISION_BF16, PRECISION_F32 = 0, 1            # enum xalm_precision
 
@@ -422,4 +430,84 @@ def rows_act(x, w, act=0, cap=0.0, mul=None, mul_act=2, w_bf16=False):
     T, K = x.shape
     out = np.empty((T, w.shape[0]), dtype=np.float32)
     check(lib().xalm_cuda_rows_act(_p(out), _p(x), _p(w), T, w.shape[0], K, act, cap, _pn(mul), mul_act, int(w_bf16)))
+    return out
+
+
+def norm_conv(x, w, cw, hist, groups, eps=1e-5):
+    """w (readers, W), cw (readers, W, taps), hist (readers, taps - 1, W).  Returns (out (readers, T, W), new hist); hist is not modified."""
+    x, w, cw = _f(x), _f(w), _f(cw)
+    readers, W, taps = cw.shape
+    T = x.shape[0]
+    hs = np.zeros((readers, max(taps - 1, 1), W), dtype=np.float32)
+    hs[:, :taps - 1] = hist
+    out = np.empty((readers, T, W), dtype=np.float32)
+    check(lib().xalm_cuda_norm_conv(_p(out), _p(hs), _p(x), T, W, groups, taps, readers, _p(w), _p(cw), eps))
+    return out, hs[:, :taps - 1]
+
+
+def short_conv(x, w, hist, bias=None, act=0):
+    """Returns (out (T, C), new hist (taps - 1, C)); hist is not modified."""
+    x, w, bias = _f(x), _f(w), _f(bias)
+    T, Cn = x.shape
+    taps = w.shape[1]
+    hs = np.zeros((max(taps - 1, 1), Cn), dtype=np.float32)
+    hs[:taps - 1] = hist
+    out = np.empty((T, Cn), dtype=np.float32)
+    check(lib().xalm_cuda_short_conv(_p(out), _p(hs), _p(x), T, Cn, taps, _p(w), _pn(bias), act))
+    return out, hs[:taps - 1]
+
+
+def embed_pair(tokens, prev, table, scale=1.0, pair=None, mul_prev=0, mul_cur=0, w=None, groups=1, eps=1e-5):
+    table, pair, w = _f(table), _f(pair), _f(w)
+    tokens = np.ascontiguousarray(tokens, dtype=np.int32)
+    V, W = table.shape
+    out = np.empty((len(tokens), W), dtype=np.float32)
+    check(lib().xalm_cuda_embed_pair(_p(out), _p(tokens), len(tokens), -1 if prev is None else prev, _p(table), V, _pn(pair),
+                                     0 if pair is None else pair.shape[0] - 1, mul_prev, mul_cur, scale, _pn(w), groups, W, eps))
+    return out
+
+
+def keyed_recurrence(q, k, v, f, state, H, rep, d, dv, mode, q_scale=0.0, dt_bias=None, A_log=None, skip=None, norm_w=None, gate=None, eps=1e-5):
+    """Returns (out (T, H dv), new state); `state` (H, d, dv) is not modified."""
+    q, k, v, f, dt_bias, A_log, skip, norm_w, gate = (_f(a) for a in (q, k, v, f, dt_bias, A_log, skip, norm_w, gate))
+    st = np.array(state, dtype=np.float32, copy=True)
+    T = q.shape[0]
+    out = np.empty((T, H * dv), dtype=np.float32)
+    check(lib().xalm_cuda_keyed_recurrence(_p(out), _p(st), _p(q), _p(k), _p(v), _p(f), T, H, rep, d, dv, mode, q_scale, _pn(dt_bias), _pn(A_log),
+                                           _pn(skip), _pn(norm_w), _pn(gate), eps))
+    return out, st
+
+
+def sink_attention(q, k, v, pos0, H, G, d, dv, scale, sink=None, out_scale=0.0, n_splits=1, cache_bf16=False):
+    q, k, v, sink = _f(q), _f(k), _f(v), _f(sink)
+    T = q.shape[0]
+    out = np.empty((T, H * dv), dtype=np.float32)
+    check(lib().xalm_cuda_sink_attention(_p(out), _p(q), _p(k), _p(v), T, pos0, H, G, d, dv, scale, _pn(sink), out_scale, n_splits, int(cache_bf16)))
+    return out
+
+
+def qk_post(proj, pos0, H, G, d, freq=None, rot_mag=0.0, ring=None):
+    """Returns (turned q rows, cache of turned keys, cache of the keys as they came), the caches row by row."""
+    proj, freq = _f(proj), _f(freq)
+    T = proj.shape[0]
+    ring = pos0 + T if ring is None else ring
+    q, kc, vc = np.empty((T, H * d), dtype=np.float32), np.empty((ring, G * d), dtype=np.float32), np.empty((ring, G * d), dtype=np.float32)
+    check(lib().xalm_cuda_qk_post(_p(q), _p(kc), _p(vc), _p(proj), T, pos0, H, G, d, _pn(freq), 0 if freq is None else freq.shape[0], rot_mag, ring))
+    return q, kc, vc
+
+
+def rows_act_bias(x, w, act, bias=None, act_pow=1.0, w_bf16=False):
+    x, w, bias = _f(x), _f(w), _f(bias)
+    T, K = x.shape
+    out = np.empty((T, w.shape[0]), dtype=np.float32)
+    check(lib().xalm_cuda_rows_act_bias(_p(out), _p(x), _p(w), T, w.shape[0], K, act, _pn(bias), act_pow, int(w_bf16)))
+    return out
+
+
+def gated_group_norm(y, w, groups, gate=None, eps=1e-5, out_scale=0.0, ld_out=None):
+    y, w, gate = _f(y), _f(w), _f(gate)
+    T, W = y.shape
+    ld_out = W if ld_out is None else ld_out
+    out = np.zeros((T, ld_out), dtype=np.float32)
+    check(lib().xalm_cuda_gated_group_norm(_p(out), _p(y), _pn(gate), _p(w), T, W, groups, eps, out_scale, ld_out))
     return out

@@ -12,6 +12,7 @@
 #include "family.h"
 #include "mix_ops.cuh"
 #include "delta_ops.cuh"
+#include "conv_ops.cuh"
 #include "latent_ops.cuh"
 #include "moe_ops.cuh"
 
@@ -61,7 +62,7 @@ uint16_t bf16_bits(float f) {
 
 static int swa_attention_op(float* out, const float* q, const float* gate, const float* k, const float* v, int T, int pos0, int H, int G, int d, int dv,
                             int window, int keep_first, float scale, float softcap, const float* r1, const float* r2, const float* talk, int ring, int n_splits,
-                            int cache_bf16) {
+                            int cache_bf16, const float* sink = nullptr, float out_scale = 0.f) {
 	if (!out || !q || !k || !v || T <= 0 || pos0 < 0 || H <= 0 || G <= 0 || H % G || d <= 0 || dv <= 0 || window <= 0 || n_splits < 1 || keep_first < 0)
 		return set_error(XALM_ERR_INVALID, "swa_attention: bad argument");
 	const int n = pos0 + T;
@@ -99,6 +100,7 @@ static int swa_attention_op(float* out, const float* q, const float* gate, const
 	a.ring = ring; a.keep_first = keep_first; a.H = H; a.G = G; a.d = d; a.dv = dv; a.window = window; a.scale = scale; a.softcap = softcap;
 	a.r1 = pool.put(r1, (size_t) H); a.r2 = pool.put(r2, (size_t) H); a.talk = pool.put(talk, (size_t) H * H);
 	a.step = pool.put(&st, 1);
+	a.sink = pool.put(sink, (size_t) H); a.out_scale = out_scale;
 	float* d_out = pool.raw<float>((size_t) T * H * dv);
 	a.out = d_out;
 	a.n_splits = n_splits;
@@ -243,15 +245,18 @@ int xalm_cuda_group_norm_residual(float* x_out, float* avg_out, const float* y, 
 	return XALM_OK;
 }
 
-int xalm_cuda_qkv_post(float* q_out, float* k_out, float* v_out, const float* proj, int T, int pos0, int H, int G, int d, int dv, const float* bq,
-                       const float* bk, const float* bv, const float* freq, int rot_half, int norm_qk, int norm_v, float eps, int keep_first, int ring) {
+static int qkv_post_op(float* q_out, float* k_out, float* v_out, const float* proj, int T, int pos0, int H, int G, int d, int dv, const float* bq,
+                       const float* bk, const float* bv, const float* freq, int rot_half, int norm_qk, int norm_v, float eps, int keep_first, int ring,
+                       float rot_mag, int v_from_k) {
 	if (!q_out || !k_out || !v_out || !proj || T <= 0 || pos0 < 0 || H <= 0 || G <= 0 || d <= 0 || dv <= 0 || 2 * rot_half > d || keep_first < 0 || ring < 1)
 		return set_error(XALM_ERR_INVALID, "qkv_post: bad argument");
 	Pool pool;
-	const int ld = H * d + G * d + G * dv, slots = keep_first + ring;
+	if (v_from_k && dv != d) return set_error(XALM_ERR_INVALID, "qkv_post: values that are the keys have the keys' size");
+	const int ld = H * d + G * d + (v_from_k ? 0 : G * dv), slots = keep_first + ring;
 	const SeqStep st = {pos0, T};
 	QkvPostArgs a = {};
-	a.proj = pool.put(proj, (size_t) T * ld); a.ld = ld; a.q_off = 0; a.k_off = H * d; a.v_off = H * d + G * d;
+	a.proj = pool.put(proj, (size_t) T * ld); a.ld = ld; a.q_off = 0; a.k_off = H * d; a.v_off = v_from_k ? H * d : H * d + G * d;
+	a.rot_mag = rot_mag;
 	a.H = H; a.G = G; a.d = d; a.dv = dv;
 	a.bq = pool.put(bq, (size_t) H * d); a.bk = pool.put(bk, (size_t) G * d); a.bv = pool.put(bv, (size_t) G * dv);
 	a.freq = rot_half ? pool.put(freq, (size_t) rot_half) : nullptr; a.rot_half = rot_half;
@@ -270,6 +275,15 @@ int xalm_cuda_qkv_post(float* q_out, float* k_out, float* v_out, const float* pr
 	XALM_CUDA_CHECK(cudaMemcpy(k_out, kc, (size_t) slots * G * d * 4, cudaMemcpyDeviceToHost));
 	XALM_CUDA_CHECK(cudaMemcpy(v_out, vc, (size_t) slots * G * dv * 4, cudaMemcpyDeviceToHost));
 	return XALM_OK;
+}
+
+int xalm_cuda_qkv_post(float* q_out, float* k_out, float* v_out, const float* proj, int T, int pos0, int H, int G, int d, int dv, const float* bq,
+                       const float* bk, const float* bv, const float* freq, int rot_half, int norm_qk, int norm_v, float eps, int keep_first, int ring) {
+	return qkv_post_op(q_out, k_out, v_out, proj, T, pos0, H, G, d, dv, bq, bk, bv, freq, rot_half, norm_qk, norm_v, eps, keep_first, ring, 0.f, 0);
+}
+int xalm_cuda_qk_post(float* q_out, float* k_out, float* v_out, const float* proj, int T, int pos0, int H, int G, int d, const float* freq, int rot_half,
+                      float rot_mag, int ring) {
+	return qkv_post_op(q_out, k_out, v_out, proj, T, pos0, H, G, d, d, nullptr, nullptr, nullptr, freq, rot_half, 0, 0, 0.f, 0, ring, rot_mag, 1);
 }
 
 int xalm_cuda_delta_rule(float* out, float* state, float* conv_state, const float* q, const float* k, const float* v, const float* gate, const float* b,
@@ -552,6 +566,150 @@ int xalm_cuda_rows_act(float* out, const float* x, const float* w, int T, int N,
 	XALM_TRY(launch_rows(d_x, K, d_w, w_bf16 != 0, T, N, K, e, nullptr));
 	XALM_TRY(finish("rows_act"));
 	XALM_CUDA_CHECK(cudaMemcpy(out, d_out, (size_t) T * N * 4, cudaMemcpyDeviceToHost));
+	return XALM_OK;
+}
+
+
+int xalm_cuda_sink_attention(float* out, const float* q, const float* k, const float* v, int T, int pos0, int H, int G, int d, int dv, float scale,
+                             const float* sink, float out_scale, int n_splits, int cache_bf16) {
+	return swa_attention_op(out, q, nullptr, k, v, T, pos0, H, G, d, dv, 0x7fffffff, 0, scale, 0.f, nullptr, nullptr, nullptr, pos0 + T, n_splits, cache_bf16, sink,
+	                        out_scale);
+}
+
+int xalm_cuda_norm_conv(float* out, float* hist, const float* x, int T, int W, int groups, int taps, int readers, const float* w, const float* cw, float eps) {
+	if (!out || !hist || !x || !w || !cw || T <= 0 || W <= 0 || readers < 1 || readers > 2) return set_error(XALM_ERR_INVALID, "norm_conv: bad argument");
+	Pool pool;
+	const size_t hw = (size_t) std::max(taps - 1, 1) * W;
+	const SeqStep st = {0, T};
+	NormConvArgs a = {};
+	a.x = pool.put(x, (size_t) T * W); a.width = W; a.groups = groups; a.taps = taps; a.readers = readers; a.eps = eps;
+	const float *d_w = pool.put(w, (size_t) readers * W), *d_cw = pool.put(cw, (size_t) readers * W * taps);
+	float *d_hist = pool.put(hist, readers * hw), *d_stage = pool.raw<float>(readers * hw), *d_out = pool.raw<float>((size_t) readers * T * W);
+	a.step = pool.put(&st, 1);
+	if (!a.x || !d_w || !d_cw || !d_hist || !d_stage || !d_out || !a.step) return set_error(XALM_ERR_CUDA, "norm_conv: device allocation failed");
+	for (int r = 0; r < readers; r++) {
+		a.w[r] = d_w + (size_t) r * W; a.cw[r] = d_cw + (size_t) r * W * taps;
+		a.hist[r] = d_hist + r * hw; a.stage[r] = d_stage + r * hw; a.out[r] = d_out + (size_t) r * T * W;
+	}
+	XALM_TRY(norm_conv_prepare(W, taps, groups));
+	XALM_TRY(launch_norm_conv(a, T, nullptr));
+	XALM_TRY(finish("norm_conv"));
+	XALM_CUDA_CHECK(cudaMemcpy(out, d_out, (size_t) readers * T * W * 4, cudaMemcpyDeviceToHost));
+	XALM_CUDA_CHECK(cudaMemcpy(hist, d_hist, readers * hw * 4, cudaMemcpyDeviceToHost));
+	return XALM_OK;
+}
+
+int xalm_cuda_short_conv(float* out, float* hist, const float* x, int T, int C, int taps, const float* w, const float* bias, int act) {
+	if (!out || !hist || !x || !w || T <= 0 || C <= 0) return set_error(XALM_ERR_INVALID, "short_conv: bad argument");
+	Pool pool;
+	const size_t hw = (size_t) std::max(taps - 1, 1) * C;
+	const SeqStep st = {0, T};
+	ShortConvArgs a = {};
+	a.in = pool.put(x, (size_t) T * C); a.ld_in = C; a.ld_out = C; a.C = C; a.taps = taps;
+	a.out = pool.raw<float>((size_t) T * C);
+	a.w = pool.put(w, (size_t) C * taps); a.bias = pool.put(bias, (size_t) C); a.act = act;
+	a.hist = pool.put(hist, hw); a.stage = pool.raw<float>(hw);
+	a.step = pool.put(&st, 1);
+	if (!a.in || !a.out || !a.w || !a.hist || !a.stage || !a.step) return set_error(XALM_ERR_CUDA, "short_conv: device allocation failed");
+	XALM_TRY(launch_short_conv(a, T, nullptr));
+	XALM_TRY(finish("short_conv"));
+	XALM_CUDA_CHECK(cudaMemcpy(out, a.out, (size_t) T * C * 4, cudaMemcpyDeviceToHost));
+	XALM_CUDA_CHECK(cudaMemcpy(hist, a.hist, hw * 4, cudaMemcpyDeviceToHost));
+	return XALM_OK;
+}
+
+int xalm_cuda_embed_pair(float* out, const int* tokens, int T, int prev, const float* table, int vocab, const float* pair, int buckets, int mul_prev,
+                         int mul_cur, float scale, const float* w, int groups, int W, float eps) {
+	if (!out || !tokens || !table || T <= 0 || vocab <= 0 || W <= 0) return set_error(XALM_ERR_INVALID, "embed_pair: bad argument");
+	Pool pool;
+	const SeqStep st = {0, T, prev};
+	EmbedPairArgs a = {};
+	a.table = pool.put(table, (size_t) vocab * W); a.pair = pool.put(pair, (size_t) (buckets + 1) * W);
+	a.scale = scale; a.mul_prev = mul_prev; a.mul_cur = mul_cur; a.buckets = buckets;
+	a.w = pool.put(w, (size_t) W); a.groups = groups; a.width = W; a.eps = eps;
+	a.tokens = pool.put(tokens, (size_t) T); a.step = pool.put(&st, 1);
+	a.x = pool.raw<float>((size_t) T * W);
+	if (!a.table || !a.tokens || !a.step || !a.x || (pair && !a.pair)) return set_error(XALM_ERR_CUDA, "embed_pair: device allocation failed");
+	XALM_TRY(launch_embed_pair(a, false, T, nullptr));
+	XALM_TRY(finish("embed_pair"));
+	XALM_CUDA_CHECK(cudaMemcpy(out, a.x, (size_t) T * W * 4, cudaMemcpyDeviceToHost));
+	return XALM_OK;
+}
+
+int xalm_cuda_keyed_recurrence(float* out, float* state, const float* q, const float* k, const float* v, const float* f, int T, int H, int rep, int d, int dv,
+                               int mode, float q_scale, const float* dt_bias, const float* A_log, const float* skip, const float* norm_w, const float* gate,
+                               float eps) {
+	if (!out || !state || !q || !k || !v || !f || T <= 0 || H <= 0 || rep <= 0 || H % rep || d <= 0 || dv <= 0 || (mode != 1 && mode != 2) ||
+	    (mode == 2 && (!dt_bias || !A_log)))
+		return set_error(XALM_ERR_INVALID, "keyed_recurrence: bad argument");
+	const size_t smem = hgrn2_smem_bytes(d, dv);
+	if (!hgrn2_cols_ok(d, dv, T, true) && (smem > 200 * 1024 || dv > 1024)) return set_error(XALM_ERR_UNSUPPORTED, "keyed_recurrence: a head's state needs %zu bytes of shared memory", smem);
+	Pool pool;
+	const int nqk = H / rep * d, nf = mode == 1 ? H * d : H;
+	const int ld = 2 * nqk + 2 * H * dv + nf; // q | k | v | gate | decays or step sizes
+	std::vector<float> proj((size_t) T * ld, 0.f);
+	for (int t = 0; t < T; t++) {
+		float* row = &proj[(size_t) t * ld];
+		memcpy(row, q + (size_t) t * nqk, (size_t) nqk * 4);
+		memcpy(row + nqk, k + (size_t) t * nqk, (size_t) nqk * 4);
+		memcpy(row + 2 * nqk, v + (size_t) t * H * dv, (size_t) H * dv * 4);
+		if (gate) memcpy(row + 2 * nqk + H * dv, gate + (size_t) t * H * dv, (size_t) H * dv * 4);
+		memcpy(row + 2 * nqk + 2 * H * dv, f + (size_t) t * nf, (size_t) nf * 4);
+	}
+	const SeqStep st = {0, T};
+	Hgrn2Args a = {};
+	a.proj = pool.put(proj.data(), proj.size()); a.ld = ld; a.q_off = 0; a.k_off = nqk; a.v_off = 2 * nqk;
+	a.f_off = a.dt_off = 2 * nqk + 2 * H * dv;
+	a.H = H; a.d = d; a.dv = dv; a.keyed = mode; a.qk_rep = rep; a.q_scale = q_scale;
+	a.dt_bias = pool.put(dt_bias, (size_t) H); a.A_log = pool.put(A_log, (size_t) H); a.skip = pool.put(skip, (size_t) H);
+	a.norm_w = pool.put(norm_w, (size_t) dv); a.eps = eps;
+	if (gate) { a.gate = a.proj; a.ldg = ld; a.g_off = 2 * nqk + H * dv; }
+	a.state = pool.put(state, (size_t) H * d * dv);
+	a.step = pool.put(&st, 1);
+	a.out = pool.raw<float>((size_t) T * H * dv);
+	a.max_rows = T;
+	if (!a.proj || !a.state || !a.step || !a.out) return set_error(XALM_ERR_CUDA, "keyed_recurrence: device allocation failed");
+	XALM_TRY(hgrn2_prepare(d, dv));
+	XALM_TRY(launch_hgrn2(a, nullptr));
+	XALM_TRY(finish("keyed_recurrence"));
+	XALM_CUDA_CHECK(cudaMemcpy(out, a.out, (size_t) T * H * dv * 4, cudaMemcpyDeviceToHost));
+	XALM_CUDA_CHECK(cudaMemcpy(state, a.state, (size_t) H * d * dv * 4, cudaMemcpyDeviceToHost));
+	return XALM_OK;
+}
+
+int xalm_cuda_rows_act_bias(float* out, const float* x, const float* w, int T, int N, int K, int act, const float* bias, float act_pow, int w_bf16) {
+	if (!out || !x || !w || T <= 0 || N <= 0 || K <= 0) return set_error(XALM_ERR_INVALID, "rows_act_bias: bad argument");
+	Pool pool;
+	void* d_w;
+	if (w_bf16) {
+		std::vector<uint16_t> wb((size_t) N * K);
+		for (size_t i = 0; i < wb.size(); i++) wb[i] = bf16_bits(w[i]);
+		d_w = pool.put(wb.data(), wb.size());
+	} else d_w = pool.put(w, (size_t) N * K);
+	const float* d_x = pool.put(x, (size_t) T * K);
+	float* d_out = pool.raw<float>((size_t) T * N);
+	RowsEpi e;
+	e.kind = EPI_ACT; e.act = act; e.bias = pool.put(bias, (size_t) N); e.act_pow = act_pow; e.out = d_out; e.ldo = N;
+	if (!d_w || !d_x || !d_out || (bias && !e.bias)) return set_error(XALM_ERR_CUDA, "rows_act_bias: device allocation failed");
+	XALM_TRY(launch_rows(d_x, K, d_w, w_bf16 != 0, T, N, K, e, nullptr));
+	XALM_TRY(finish("rows_act_bias"));
+	XALM_CUDA_CHECK(cudaMemcpy(out, d_out, (size_t) T * N * 4, cudaMemcpyDeviceToHost));
+	return XALM_OK;
+}
+
+int xalm_cuda_gated_group_norm(float* out, const float* y, const float* gate, const float* w, int T, int W, int groups, float eps, float out_scale, int ld_out) {
+	if (!out || !y || !w || T <= 0 || W <= 0 || ld_out < W) return set_error(XALM_ERR_INVALID, "gated_group_norm: bad argument");
+	Pool pool;
+	GroupNormArgs g;
+	g.y = pool.put(y, (size_t) T * W); g.ldy = W;
+	g.gate = pool.put(gate, (size_t) T * W); g.ldg = W;
+	g.w = pool.put(w, (size_t) W); g.groups = groups; g.width = W; g.eps = eps; g.out_scale = out_scale;
+	g.x_out = pool.raw<float>((size_t) T * ld_out); g.ld_out = ld_out;
+	if (!g.y || !g.w || !g.x_out || (gate && !g.gate)) return set_error(XALM_ERR_CUDA, "gated_group_norm: device allocation failed");
+	XALM_TRY(group_norm_prepare(W, groups));
+	XALM_TRY(launch_group_norm(g, T, nullptr));
+	XALM_TRY(finish("gated_group_norm"));
+	XALM_CUDA_CHECK(cudaMemcpy(out, g.x_out, (size_t) T * ld_out * 4, cudaMemcpyDeviceToHost));
 	return XALM_OK;
 }
 
