@@ -528,6 +528,60 @@ def build_duletar(z: dict, seed: int, max_tokens: int, stream):
     return m
 
 
+def kubolorn_config(z: dict) -> dict:
+    """Layers alternate: attention (no window, values = keys, rotation on half of each head with YaRN rescaling, sinks) beside a state-space
+    mixer, with a dense feed-forward; then gated linear attention with a mixture of 16 relu-squared experts of ff / 4 of which 4 are chosen (as
+    many active feed-forward weights as the dense layer needs for one of its two matrices).  Both sublayers read through 4-tap convolutions."""
+    att = {"heads": z["heads"], "kv_heads": z["kv_heads"], "dim": z["head_dim"], "vdim": z["head_dim"], "scale": z["head_dim"] ** -0.5,
+           "rot": {"base": 10000.0, "dims": z["head_dim"] // 2, "scaling": {"factor": 8.0, "fast": 16.0, "slow": 2.0, "original": 8192}}}
+    ssd = {"heads": 2 * z["r_heads"], "vdim": z["r_vdim"], "state": z["r_dim"], "groups": z["r_heads"], "conv": 4, "norm_groups": 4}
+    gla = {"heads": 2 * z["r_heads"], "dim": z["r_dim"], "vdim": z["r_vdim"], "tau": 8.0}
+    moe = {"kind": "moe", "expert": {"ff": z["ff"] // 4}, "router": {"experts": 16, "top": 4}}
+    pair = [{"type": "parallel", "mixer": {"left": att, "right": ssd, "left_scale": 1.0, "right_scale": 0.7}, "mlp": {"kind": "dense", "ff": z["ff"]}},
+            {"type": "gla", "mixer": gla, "mlp": moe}]
+    return {"architecture": "Kubolorn", "vocab": z["vocab"], "width": z["width"], "norm": {"eps": 1e-6, "groups": 8}, "canon": {"taps": 4},
+            "embedding": {"scale": float(z["width"]) ** 0.5, "bigram": {"buckets": 8191, "mul_prev": 1000003, "mul_cur": 7919}},
+            "layers": (pair * z["layers"])[:z["layers"]]}
+
+
+def build_kubolorn(z: dict, seed: int, max_tokens: int, stream):
+    """Random bf16 weights, uploaded tensor by tensor as the backend names them (the decay's inner size, 32, is the tensors')."""
+    import ctypes as C
+    import json
+    from xalm_b200 import capi, safetensors_io as ST, types as T
+    from xalm_b200.model import Model
+    m = Model._from_json_text(json.dumps(kubolorn_config(z)), {})
+    L = capi.lib()
+    h = C.c_void_p()
+    capi.check(L.xalm_cuda_create_json(m.config["json"].encode(), 0, max_tokens, capi.PRECISION_BF16, C.byref(h)))
+    m._h = h
+    capi.check(L.xalm_cuda_set_stream(h, C.c_void_p(stream)))
+    rng = np.random.default_rng(seed)
+    for name, shape in m.expected_tensors().items():
+        shape = tuple(32 if d < 0 else d for d in shape)
+        leaf = name.split(".")[-1]
+        if leaf in ("conv", "canon1", "canon2"):
+            a = 0.3 * rng.standard_normal(shape, dtype=np.float32)
+        elif name in ("embed", "bigram"):
+            a = rng.standard_normal(shape, dtype=np.float32) * np.float32(1.0 / np.sqrt(shape[1]))   # times sqrt(width) in the model: rows of order one
+        elif len(shape) == 2:
+            a = rng.standard_normal(shape, dtype=np.float32) * np.float32((2.0 if leaf == "router" else 1.0) / np.sqrt(shape[1]))
+        elif leaf == "A_log":
+            a = rng.uniform(-3.0, 0.0, shape).astype(np.float32)
+        elif leaf in ("dt_bias", "sink"):
+            a = 0.2 * rng.standard_normal(shape, dtype=np.float32)
+        elif leaf == "b":
+            a = (3.0 + rng.standard_normal(shape, dtype=np.float32)) if name.endswith("a2.b") else 0.1 * rng.standard_normal(shape, dtype=np.float32)
+        elif leaf in ("norm1", "norm2"):
+            a = 0.3 + 0.05 * rng.standard_normal(shape, dtype=np.float32)
+        else:
+            a = 1.0 + 0.1 * rng.standard_normal(shape, dtype=np.float32)
+        m.upload(name, T.BF16, shape, ST.f32_to_bf16_bits(a).view(np.uint8).reshape(-1))
+    capi.check(L.xalm_cuda_finalize(h))
+    m.config["vocab_size"] = z["vocab"]
+    return m
+
+
 def run_family_workload(args, fams=("nabalix", "llama")):
     """Prefill and one-token-step throughput of config.json families beside one another and beside the Llama family at equal layer sizes
     (bf16 weights, random), device-timed with CUDA events on the launching stream.  One JSON line; `value` is the first family's decode rate
@@ -552,7 +606,7 @@ def run_family_workload(args, fams=("nabalix", "llama")):
             for fam in fams:
                 if fam != "llama":
                     capi.tune("seq_chunk", args.seq_chunk)  # positions per pass of a prompt (the Llama arm takes the prompt in one pass)
-                    m = {"nabalix": build_nabalix, "bolovik": build_bolovik, "duletar": build_duletar}[fam](z, args.seed, ctx, stream.cuda_stream)
+                    m = {"nabalix": build_nabalix, "bolovik": build_bolovik, "duletar": build_duletar, "kubolorn": build_kubolorn}[fam](z, args.seed, ctx, stream.cuda_stream)
                 else:
                     m, _ = build_model_streaming(llama_full, llama_cfg, T.BF16, args.seed, False, stream=stream.cuda_stream)
                     capi.tune("prefill_split", 1)        # plain fp16 operands, the counterpart of the one-plane path
@@ -613,13 +667,14 @@ def main():
     ap.add_argument("--past-window", action="store_true",
                     help="also time steps at positions >= ctx: the KV ring is full (kv_len = ctx), 2 attention sinks active (infer.cpp:608-613)")
     ap.add_argument("--no-prefill", action="store_true", help="skip the perplexity-mode summary appended to the decode line at N=1")
-    ap.add_argument("--workload", default="decode", choices=["decode", "perplexity", "families", "bolovik", "duletar"],
+    ap.add_argument("--workload", default="decode", choices=["decode", "perplexity", "families", "bolovik", "duletar", "kubolorn"],
                     help="decode = BASELINE config[1] (the headline metric); perplexity = config[2]: batched prefill of a 4k-token input; "
                          "families = prefill and one-token-step throughput of the Nabalix family beside the Llama family at equal layer sizes; "
                          "bolovik = the same for the Bolovik family beside the Nabalix and Llama families; "
-                         "duletar = the same for the Duletar family beside the Bolovik family")
-    ap.add_argument("--arms", default="", help="bolovik / duletar workloads: which families run, the first one is the headline "
-                                               "(default bolovik,nabalix,llama / duletar,bolovik)")
+                         "duletar = the same for the Duletar family beside the Bolovik family; "
+                         "kubolorn = the same for the Kubolorn family beside the Bolovik family")
+    ap.add_argument("--arms", default="", help="bolovik / duletar / kubolorn workloads: which families run, the first one is the headline "
+                                               "(default bolovik,nabalix,llama / duletar,bolovik / kubolorn,bolovik)")
     ap.add_argument("--seq-chunk", type=int, default=1024, help="families workload: positions per pass of a Nabalix prompt")
     ap.add_argument("--sizes", default="w1024,w2048,w4096", help="families workload: which of " + ",".join(FAMILY_SIZES))
     ap.add_argument("--tokens", type=int, default=4096, help="perplexity workload: tokens per step")
@@ -630,9 +685,9 @@ def main():
     if args.workload == "perplexity":
         run_perplexity_workload(args)
         return
-    if args.workload in ("families", "bolovik", "duletar"):
+    if args.workload in ("families", "bolovik", "duletar", "kubolorn"):
         if not args.arms:
-            args.arms = "duletar,bolovik" if args.workload == "duletar" else "bolovik,nabalix,llama"
+            args.arms = {"duletar": "duletar,bolovik", "kubolorn": "kubolorn,bolovik"}.get(args.workload, "bolovik,nabalix,llama")
         if args.steps == 256:
             args.steps = 64
         if args.tokens == 4096:
